@@ -30,6 +30,11 @@ class PagedNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every past token stays visible
+    v_head_dim: Optional[int] = None  # size of a value row when it differs from a key row's (None: head_dim)
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -51,12 +56,30 @@ class CacheGroup:
         self.allocator = PageAllocator(num_pages)
         self.tables: Dict[Hashable, List[int]] = {}
         self.pool = None            # device tensor [len(layers), 2, num_pages, kv_heads, page_size, head_dim]
+        self.pool_k = None          # keys and values of different row sizes live in two tensors instead:
+        self.pool_v = None          # [len(layers), num_pages, kv_heads, page_size, head_dim | v_head_dim]
 
     def layer_index(self, layer: int) -> int:
         return self.layers.index(layer)
 
+    def allocate(self, dtype, device) -> None:
+        import torch
+        n, nd, P = len(self.layers), self.need, self.allocator.num_pages
+        if nd.value_dim == nd.head_dim:
+            self.pool = torch.zeros((n, 2, P, nd.kv_heads, self.page_size, nd.head_dim), dtype=dtype, device=device)
+        else:
+            self.pool_k = torch.zeros((n, P, nd.kv_heads, self.page_size, nd.head_dim), dtype=dtype, device=device)
+            self.pool_v = torch.zeros((n, P, nd.kv_heads, self.page_size, nd.value_dim), dtype=dtype, device=device)
+
+    def k_pages(self, li: int):
+        """[num_pages, kv_heads, page_size, head_dim] of the group's li-th layer."""
+        return self.pool[li, 0] if self.pool is not None else self.pool_k[li]
+
+    def v_pages(self, li: int):
+        return self.pool[li, 1] if self.pool is not None else self.pool_v[li]
+
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.layers) * self.need.kv_heads * self.need.head_dim * element_size
+        return len(self.layers) * self.need.kv_heads * (self.need.head_dim + self.need.value_dim) * element_size
 
 
 @dataclass
@@ -69,7 +92,8 @@ class _Live:
 class CacheManager:
     def __init__(self, layer_needs: Dict[int, object], *, page_size: int, num_pages, max_num_seqs: int,
                  dtype=None, device=None, allocate: bool = True):
-        """``layer_needs``: layer index -> PagedNeed | StateNeed | None.
+        """``layer_needs``: cache unit (a layer's index, or the id of a run's private cache) ->
+        PagedNeed | StateNeed | a list of both | None.
         ``num_pages``: pages of every group, or a dict group-key -> pages."""
         import torch
 
@@ -83,12 +107,17 @@ class CacheManager:
             need = layer_needs[layer]
             if need is None:
                 continue
-            if isinstance(need, PagedNeed):
-                by_need.setdefault(need, []).append(layer)
-            elif isinstance(need, StateNeed):
-                self.state_layers[layer] = need
-            else:
-                raise TypeError(f"layer {layer}: unknown cache need {need!r}")
+            # a mixer with several branches may need pages and a state: a list with at most one of each
+            several = list(need) if isinstance(need, (list, tuple)) else [need]
+            if sum(isinstance(n, PagedNeed) for n in several) > 1 or sum(isinstance(n, StateNeed) for n in several) > 1:
+                raise TypeError(f"layer {layer}: at most one PagedNeed and one StateNeed per layer, got {need!r}")
+            for nd in several:
+                if isinstance(nd, PagedNeed):
+                    by_need.setdefault(nd, []).append(layer)
+                elif isinstance(nd, StateNeed):
+                    self.state_layers[layer] = nd
+                elif nd is not None:
+                    raise TypeError(f"layer {layer}: unknown cache need {nd!r}")
         for need, layers in by_need.items():
             n = num_pages[need] if isinstance(num_pages, dict) else int(num_pages)
             g = CacheGroup(len(self.groups), need, layers, n, page_size)
@@ -102,9 +131,7 @@ class CacheManager:
         self.device = device
         if allocate:
             for g in self.groups:
-                g.pool = torch.zeros(
-                    (len(g.layers), 2, g.allocator.num_pages, g.need.kv_heads, page_size, g.need.head_dim),
-                    dtype=dtype, device=device)
+                g.allocate(dtype, device)
             for layer, need in self.state_layers.items():
                 self.states[layer] = torch.zeros((max_num_seqs,) + tuple(need.shape),
                                                  dtype=getattr(torch, need.dtype), device=device)

@@ -116,10 +116,13 @@ def registered_architectures():
 
 
 def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
-    """Pick the architecture named by ``architectures`` and parse its keys."""
+    """Pick the architecture named by ``architectures`` (a list, the first registered name wins) or
+    ``architecture`` (one name) and parse its keys."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json has no 'architectures' list")
+        raise ConfigError("config.json has neither an 'architectures' list nor an 'architecture' name")
     last_err: Optional[Exception] = None
     for name in archs:
         if name in _ARCHITECTURES:

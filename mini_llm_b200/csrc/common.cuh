@@ -11,7 +11,7 @@
 // dtype codes used across the C interface
 enum { MLLM_F32 = 0, MLLM_BF16 = 1 };
 // epilogue activation codes
-enum { MLLM_ACT_NONE = 0, MLLM_ACT_GELU_TANH = 1, MLLM_ACT_GELU_ERF = 2 };
+enum { MLLM_ACT_NONE = 0, MLLM_ACT_GELU_TANH = 1, MLLM_ACT_GELU_ERF = 2, MLLM_ACT_RELU = 3, MLLM_ACT_SILU = 4 };
 
 // Records a message for mllm_last_error() and returns the code.
 int mllm_fail(int code, const char* fmt, ...);

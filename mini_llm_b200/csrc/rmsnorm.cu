@@ -1,0 +1,141 @@
+// RMS norm of 32-bit rows: y = x / sqrt(mean(x^2) + eps) * (w + offset), optionally of gathered rows,
+// written as 32-bit or bfloat16.  `offset` is 1 for weights that are stored around zero and 0 for plain
+// weights.  A second weight vector and output may be given: two norms of the same rows that differ only
+// in their weights (the two branches of a parallel block) then cost one read of x and one sum of squares.
+// All arithmetic is 32-bit; the sum of squares runs in an order that depends on the width only.
+#include "common.cuh"
+
+namespace {
+
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* x, long long x_stride, const int* __restrict__ rows,
+                               const float* __restrict__ w1, const float* __restrict__ w2, TOut* __restrict__ out1,
+                               TOut* __restrict__ out2, int D, float eps, float offset) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+    float q = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) q = fmaf(xr[d], xr[d], q);
+    const float inv = 1.0f / sqrtf(block_sum(q, scratch) / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float y = xr[d] * inv;
+        out1[(size_t)r * D + d] = from_f32<TOut>(y * (w1[d] + offset));
+        if (out2) out2[(size_t)r * D + d] = from_f32<TOut>(y * (w2[d] + offset));
+    }
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store4(TOut* o, float y0, float y1, float y2, float y3) {
+    if constexpr (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4*>(o) = make_float4(y0, y1, y2, y3);
+    } else {
+        uint2 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+        h[0] = __floats2bfloat162_rn(y0, y1);
+        h[1] = __floats2bfloat162_rn(y2, y3);
+        *reinterpret_cast<uint2*>(o) = pk;
+    }
+}
+
+// One warp per row, the row held in registers (up to 2048 columns), 16-byte loads and stores.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* x, long long x_stride, const int* __restrict__ rows, const float* __restrict__ w1,
+                    const float* __restrict__ w2, TOut* __restrict__ out1, TOut* __restrict__ out2, int R, int D,
+                    float eps, float offset) {
+    constexpr int KEEP = 16;
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= R) return;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+    float4 v[KEEP];
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int k = lane * 4 + i * 128;
+        v[i] = k < D ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int k = lane * 4 + i * 128;
+        if (k >= D) break;
+        const float y0 = v[i].x * inv, y1 = v[i].y * inv, y2 = v[i].z * inv, y3 = v[i].w * inv;
+        const float4 g = __ldg(reinterpret_cast<const float4*>(w1 + k));
+        store4<TOut>(out1 + (size_t)r * D + k, y0 * (g.x + offset), y1 * (g.y + offset), y2 * (g.z + offset),
+                     y3 * (g.w + offset));
+        if (out2) {
+            const float4 g2 = __ldg(reinterpret_cast<const float4*>(w2 + k));
+            store4<TOut>(out2 + (size_t)r * D + k, y0 * (g2.x + offset), y1 * (g2.y + offset), y2 * (g2.z + offset),
+                         y3 * (g2.w + offset));
+        }
+    }
+}
+
+template <typename TOut>
+int launch(const float* x, long long x_stride, const int* rows, const float* w1, const float* w2, void* out1, void* out2,
+           int R, int D, float eps, float offset, cudaStream_t stream) {
+    const bool fast = D % 4 == 0 && D <= 2048 && x_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w1 % 16 == 0 &&
+                      (uintptr_t)out1 % 16 == 0 && (!out2 || ((uintptr_t)w2 % 16 == 0 && (uintptr_t)out2 % 16 == 0));
+    if (fast) {
+        MLLM_CUDA(mllm_launch(rmsnorm_warp_kernel<TOut>, dim3((R + 7) / 8), dim3(256), 0, stream, true, x, x_stride, rows,
+                              w1, w2, (TOut*)out1, (TOut*)out2, R, D, eps, offset));
+        return 0;
+    }
+    const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
+    MLLM_CUDA(mllm_launch(rmsnorm_kernel<TOut>, dim3(R), dim3(threads), 0, stream, true, x, x_stride, rows, w1, w2,
+                          (TOut*)out1, (TOut*)out2, D, eps, offset));
+    return 0;
+}
+
+// out[t][c] = act(gu[t][c]) * gu[t][F + c]: the gate and the up half of one product's output.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long long out_stride, int rows, int F, int act) {
+    pdl_wait();
+    pdl_launch();
+    const long long total = (long long)rows * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / F), c = (int)(i % F);
+        const float g = to_f32(gu[(size_t)t * gu_stride + c]), u = to_f32(gu[(size_t)t * gu_stride + F + c]);
+        float a;
+        if (act == MLLM_ACT_RELU) a = fmaxf(g, 0.f);
+        else if (act == MLLM_ACT_SILU) a = g / (1.0f + expf(-g));
+        else a = apply_act(g, act);
+        out[(size_t)t * out_stride + c] = from_f32<T>(a * u);
+    }
+}
+
+}  // namespace
+
+MLLM_EXPORT int mllm_rmsnorm(const float* x, long long x_stride, const int* rows, const float* w1, const float* w2,
+                             void* out1, void* out2, int R, int D, float eps, float offset, int out_dtype,
+                             cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (D <= 0) return mllm_fail(1, "rmsnorm: width %d", D);
+    if ((w2 == nullptr) != (out2 == nullptr)) return mllm_fail(1, "rmsnorm: the second weight and output come together");
+    if (out_dtype == MLLM_F32) return launch<float>(x, x_stride, rows, w1, w2, out1, out2, R, D, eps, offset, stream);
+    if (out_dtype == MLLM_BF16)
+        return launch<__nv_bfloat16>(x, x_stride, rows, w1, w2, out1, out2, R, D, eps, offset, stream);
+    return mllm_fail(1, "rmsnorm: unknown dtype code %d", out_dtype);
+}
+
+MLLM_EXPORT int mllm_gated_act(const void* gu, long long gu_stride, void* out, long long out_stride, int rows, int F,
+                               int act, int dtype, cudaStream_t stream) {
+    if (rows <= 0 || F <= 0) return 0;
+    const long long total = (long long)rows * F;
+    const int grid = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)gu, gu_stride,
+                              (float*)out, out_stride, rows, F, act));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(gated_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
+                              (const __nv_bfloat16*)gu, gu_stride, (__nv_bfloat16*)out, out_stride, rows, F, act));
+    else
+        return mllm_fail(1, "gated_act: unknown dtype code %d", dtype);
+    return 0;
+}

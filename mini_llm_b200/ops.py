@@ -23,7 +23,8 @@ DECODE_SPLIT = 128           # keys per split of the decode attention (csrc/atte
 DECODE_CLUSTER_SPLITS = 8    # splits that can meet in one thread-block cluster (MAX_CLUSTER there)
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
-_ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}      # what the products' epilogues take
+_GATE_ACT = {"gelu_tanh": 1, "gelu_erf": 2, "relu": 3, "silu": 4}   # what gated_act takes
 _lib = None
 
 c_int, c_ll, c_float, c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
@@ -84,6 +85,17 @@ def _signatures(lib):
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_attention_tiled_wide": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                       c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "mllm_rmsnorm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
+                         c_int, c_void_p],
+        "mllm_gated_act": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_paged_write": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_attention_bias_split_keys": [],
+        "mllm_attention_bias": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                                  c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -322,6 +334,49 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
         raise KernelError("layernorm: x and out differ in rows")
     _call("mllm_layernorm", x.data_ptr(), rows.data_ptr() if rows is not None else None, gamma.data_ptr(),
           beta.data_ptr(), out.data_ptr(), R, D, float(eps), _dt(out), _stream())
+
+
+def rmsnorm(x, weight, eps: float, out, rows=None, unit_offset: bool = True, weight2=None, out2=None) -> None:
+    """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * (weight + 1) (or * weight when ``unit_offset`` is False);
+    x 32-bit, out 32-bit or bfloat16.  ``weight2`` / ``out2``: a second norm of the same rows with other weights,
+    from the same sum of squares."""
+    _cuda("x", x, torch.float32, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    _cuda("out", out)
+    ldx = _rows("x", x)
+    D = x.shape[1]
+    R = out.shape[0]
+    if weight.numel() != D or out.shape[1] != D:
+        raise KernelError(f"rmsnorm: width {D} against weight {weight.numel()}, out {tuple(out.shape)}")
+    if (weight2 is None) != (out2 is None):
+        raise KernelError("rmsnorm: the second weight and the second output come together")
+    if weight2 is not None:
+        _cuda("weight2", weight2, torch.float32)
+        _cuda("out2", out2, out.dtype)
+        if weight2.numel() != D or tuple(out2.shape) != tuple(out.shape):
+            raise KernelError("rmsnorm: the second weight or output does not fit the first")
+    if rows is not None:
+        _cuda("rows", rows, torch.int32)
+        if rows.numel() != R:
+            raise KernelError("rmsnorm: rows and out differ in length")
+    elif x.shape[0] != R:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    _call("mllm_rmsnorm", x.data_ptr(), ldx, rows.data_ptr() if rows is not None else None, weight.data_ptr(),
+          weight2.data_ptr() if weight2 is not None else None, out.data_ptr(),
+          out2.data_ptr() if out2 is not None else None, R, D, float(eps), 1.0 if unit_offset else 0.0, _dt(out), _stream())
+
+
+def gated_act(gu, out, act: str) -> None:
+    """out[t, c] = act(gu[t, c]) * gu[t, F + c] for gu [T, 2F]: the gate and the up half of one product."""
+    _cuda("gu", gu, contiguous=False)
+    _cuda("out", out, gu.dtype, contiguous=False)
+    T, F = out.shape
+    if tuple(gu.shape) != (T, 2 * F):
+        raise KernelError(f"gated_act: gu {tuple(gu.shape)} against out {tuple(out.shape)}")
+    if act not in _GATE_ACT:
+        raise KernelError(f"gated_act: unknown activation {act!r}; known: {sorted(_GATE_ACT)}")
+    _call("mllm_gated_act", gu.data_ptr(), _rows("gu", gu), out.data_ptr(), _rows("out", out), T, F, _GATE_ACT[act],
+          _dt(gu), _stream())
 
 
 # --------------------------------------------------------------------------- linear
@@ -632,6 +687,120 @@ def kv_write(k, v, k_pages, v_pages, slot_mapping) -> None:
         raise KernelError("kv_write: shapes do not fit the pages")
     _call("mllm_kv_write", k.data_ptr(), v.data_ptr(), ld, k_pages.data_ptr(), v_pages.data_ptr(),
           slot_mapping.data_ptr(), T, Hkv, dh, ps, _dt(k), _stream())
+
+
+def paged_write(src, pages, slot_mapping) -> None:
+    """Rows of src [T, heads * d] (rows contiguous) to their slots in pages [num_pages, heads, page_size, d]."""
+    _cuda("src", src, contiguous=False)
+    _cuda("pages", pages, src.dtype)
+    _cuda("slot_mapping", slot_mapping, torch.int32)
+    _, heads, ps, d = pages.shape
+    T = src.shape[0]
+    if src.shape[1] != heads * d or slot_mapping.numel() != T:
+        raise KernelError(f"paged_write: src {tuple(src.shape)} against pages {tuple(pages.shape)}")
+    _call("mllm_paged_write", src.data_ptr(), _rows("src", src), pages.data_ptr(), slot_mapping.data_ptr(), T, heads, d,
+          ps, _dt(src), _stream())
+
+
+BIAS_ATTN_MAX_DIM = 256        # largest key and value size of csrc/attention_bias.cu
+_bias_split_keys = None
+
+
+def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, scale, dist_bias=None,
+                     q_scale=None, out_scale: float = 1.0, window=None, impl: Optional[str] = None) -> None:
+    """Causal attention over the cache with keys and values of different sizes, an additive score bias
+    ``dist_bias[head, i - j]`` (float32 [heads, n]) and a factor ``q_scale[position]`` (float32 [n]) on the query:
+    out[t] = out_scale * softmax_j((q_t . k_j) * scale * q_scale[p_t] + dist_bias[h, p_t - j]) v_j.
+
+    q [T, heads * dk], k_pages [P, kv_heads, page_size, dk], v_pages [P, kv_heads, page_size, dv],
+    out [T, heads * dv] (rows contiguous; a column slice of a wider buffer is fine).
+    """
+    global _bias_split_keys
+    _cuda("q", q, contiguous=False)
+    _cuda("k_pages", k_pages, q.dtype)
+    _cuda("v_pages", v_pages, q.dtype)
+    _cuda("out", out, q.dtype, contiguous=False)
+    _cuda("block_table", block_table, torch.int32, contiguous=False)
+    T = q.shape[0]
+    _, Hkv, ps, dk = k_pages.shape
+    dv = v_pages.shape[3]
+    if Hkv != num_kv_heads or q.shape[1] != num_heads * dk or tuple(out.shape) != (T, num_heads * dv) \
+            or v_pages.shape[:3] != k_pages.shape[:3]:
+        raise KernelError("biased_attention: head counts or sizes do not fit the pages")
+    ldq, ldo = _rows("q", q), _rows("out", out)
+    vec = 16 // q.element_size()
+    if dk % 8 != 0 or ldq % vec != 0 or q.data_ptr() % 16 != 0:
+        raise KernelError(f"biased_attention: key size {dk} must be a multiple of 8 and query rows 16-byte aligned")
+    n_dist = 0
+    if dist_bias is not None:
+        _cuda("dist_bias", dist_bias, torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != num_heads:
+            raise KernelError("biased_attention: dist_bias must be [heads, distances]")
+        n_dist = dist_bias.shape[1]
+        if ctx.max_ctx_len > n_dist:
+            raise KernelError(f"biased_attention: a context of {ctx.max_ctx_len} tokens exceeds the bias table's {n_dist} distances")
+    if q_scale is not None:
+        _cuda("q_scale", q_scale, torch.float32)
+        if ctx.max_ctx_len > q_scale.numel():
+            raise KernelError("biased_attention: a position exceeds the query-scale table")
+    if impl is None:
+        impl = "simt"
+        if getattr(ctx, "decode_only", False):
+            impl = "split"
+        elif getattr(ctx, "n_tiles", 0) > 0:
+            impl = "tiled"
+    attention_launches["bias_" + impl] = attention_launches.get("bias_" + impl, 0) + 1
+    part_o = part_ml = None
+    nsplit = 0
+    tiles, n_tiles = None, 0
+    if impl == "split":
+        if _bias_split_keys is None:
+            _bias_split_keys = int(library().mllm_attention_bias_split_keys())
+        # splits cover the longest context of the step, rounded up to a power of two so that captured graphs keep their grid
+        need = max(1, -(-int(ctx.max_ctx_len) // _bias_split_keys))
+        nsplit = 1 << (need - 1).bit_length()
+        part_o = ctx.ws.buf("battn_part_o", T * num_heads * nsplit, dv, torch.float32).data_ptr()
+        part_ml = ctx.ws.buf("battn_part_ml", T * num_heads * nsplit, 2, torch.float32).data_ptr()
+    elif impl == "tiled":
+        tiles, n_tiles = ctx.attn_tiles.data_ptr(), int(ctx.n_tiles)
+    elif impl != "simt":
+        raise KernelError(f"biased_attention: unknown implementation {impl!r}")
+    _call("mllm_attention_bias", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+          _rows("block_table", block_table), ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), tiles, n_tiles,
+          out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dk, dv, ps, float(scale),
+          float(out_scale), dist_bias.data_ptr() if dist_bias is not None else None, n_dist,
+          q_scale.data_ptr() if q_scale is not None else None, int(window or 0), _dt(q),
+          {"simt": 0, "tiled": 1, "split": 2}[impl], _stream())
+    if impl == "split":
+        global launches
+        launches += 1           # the kernel that merges the splits
+
+
+def gated_recurrence(a, z, v, f_bias, lower, norm_weight, eps: float, state, ctx, out, *, heads: int, out_scale: float = 1.0,
+                     write_state: bool = True) -> None:
+    """The gated linear recurrence of csrc/gated_recurrence.cu over the step's tokens, request by request:
+    f = lower + (1 - lower) * sigmoid(z + f_bias); S <- diag(f) S + (1 - f) v^T; o = S^T silu(a);
+    out = out_scale * rms_norm(o) * norm_weight per head.  a, z [T, heads * ek], v, out [T, heads * ev] (rows
+    contiguous; column slices are fine), state [slots, heads, ek, ev] float32, indexed by ctx.state_slots."""
+    _cuda("a", a, contiguous=False)
+    _cuda("z", z, a.dtype, contiguous=False)
+    _cuda("v", v, a.dtype, contiguous=False)
+    _cuda("out", out, a.dtype, contiguous=False)
+    _cuda("state", state, torch.float32)
+    for name, t in (("f_bias", f_bias), ("lower", lower), ("norm_weight", norm_weight)):
+        _cuda(name, t, torch.float32)
+    T = a.shape[0]
+    if state.dim() != 4 or state.shape[1] != heads:
+        raise KernelError(f"gated_recurrence: state {tuple(state.shape)} against {heads} heads")
+    ek, ev = state.shape[2], state.shape[3]
+    if tuple(a.shape) != (T, heads * ek) or tuple(z.shape) != (T, heads * ek) or tuple(v.shape) != (T, heads * ev) \
+            or tuple(out.shape) != (T, heads * ev) or f_bias.numel() != heads * ek or lower.numel() != heads * ek \
+            or norm_weight.numel() != ev:
+        raise KernelError("gated_recurrence: shapes do not fit the state")
+    _call("mllm_gated_recurrence", a.data_ptr(), _rows("a", a), z.data_ptr(), _rows("z", z), v.data_ptr(), _rows("v", v),
+          f_bias.data_ptr(), lower.data_ptr(), norm_weight.data_ptr(), state.data_ptr(), ctx.cu_q.data_ptr(),
+          ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S, heads, ek, ev, float(eps), float(out_scale),
+          int(write_state), _dt(a), _stream())
 
 
 attention_launches = {}     # attention kernel name -> launches so far (tests check which kernel a step took)

@@ -20,6 +20,7 @@ from typing import Optional
 
 from ..cache.manager import PagedNeed
 from .base import Mixer, ParamSpec, register_part
+from .projected import ProjectedMixer
 
 
 class Attention(Mixer):
@@ -89,3 +90,91 @@ class Attention(Mixer):
 
 
 register_part("mixer", "attention", Attention)
+
+
+class DistanceBiasAttention(ProjectedMixer):
+    """Causal softmax attention with grouped key/value heads, key and value heads of different sizes, no
+    rotation, and two ways in which positions enter the scores:
+
+    * a query temperature: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+      (``q_temp_coef`` = 0: none);
+    * a distance penalty per head: r1_h * ln(1 + r2_h * (i - j)) is taken off the score of query i and key j,
+      with r1, r2 learned per head (``log_distance_bias`` False: none).
+
+    Both are functions of one integer, so they are tabulated once when the weights are bound (in float64, kept
+    in float32): a factor per position and a bias per head and distance; the attention kernels look them up.
+    """
+
+    in_names = ("q_weight", "k_weight", "v_weight")
+    out_name = "out_weight"
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float,
+                 max_positions: int, q_temp_coef: float = 0.0, q_temp_every: int = 1, log_distance_bias: bool = True,
+                 window: Optional[int] = None):
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.scale = float(scale)
+        self.max_positions = int(max_positions)
+        self.q_temp_coef, self.q_temp_every = float(q_temp_coef), int(q_temp_every)
+        self.log_distance_bias = bool(log_distance_bias)
+        self.window = None if window is None else int(window)
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if self.q_temp_every < 1:
+            raise ValueError("q_temp_every must be at least 1")
+        self.q_size = self.num_heads * self.head_dim
+        self.k_size = self.num_kv_heads * self.head_dim
+        self.v_size = self.num_kv_heads * self.v_head_dim
+        self.dist_bias = None
+        self.q_scale = None
+
+    def param_specs(self):
+        p = {"q_weight": ParamSpec((self.q_size, self.hidden_size), "matrix"),
+             "k_weight": ParamSpec((self.k_size, self.hidden_size), "matrix"),
+             "v_weight": ParamSpec((self.v_size, self.hidden_size), "matrix"),
+             "out_weight": ParamSpec((self.hidden_size, self.num_heads * self.v_head_dim), "matrix")}
+        if self.log_distance_bias:
+            p["r1"] = ParamSpec((self.num_heads,), "vector")
+            p["r2"] = ParamSpec((self.num_heads,), "vector")
+        return p
+
+    def kernel_limits(self, dtype: str):
+        out = []
+        if self.head_dim % 8 != 0 or not (8 <= self.head_dim <= 256):
+            out.append(f"distance-bias attention: key size {self.head_dim} is not a multiple of 8 between 8 and 256")
+        if not (1 <= self.v_head_dim <= 256):
+            out.append(f"distance-bias attention: value size {self.v_head_dim} is not between 1 and 256")
+        return out
+
+    def cache_need(self):
+        return PagedNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
+                         v_head_dim=None if self.v_head_dim == self.head_dim else self.v_head_dim)
+
+    def bind(self, params, rt) -> None:
+        import torch
+        super().bind(params, rt)
+        if not params:
+            return
+        n = self.max_positions
+        if self.log_distance_bias:
+            d = torch.arange(n, dtype=torch.float64)[None, :]
+            r1 = self.r1.detach().double().cpu()[:, None]
+            r2 = self.r2.detach().double().cpu()[:, None]
+            self.dist_bias = (-r1 * torch.log1p(r2 * d)).float().contiguous().to(rt.device)
+        if self.q_temp_coef != 0.0:
+            steps = torch.div(torch.arange(n, dtype=torch.int64) + 1, self.q_temp_every, rounding_mode="floor").double()
+            self.q_scale = (1.0 + self.q_temp_coef * torch.log(steps + 1.0)).float().contiguous().to(rt.device)
+
+    def core(self, proj, ctx, cache, out, out_scale: float = 1.0) -> None:
+        ops = self.rt.ops
+        gv = ctx.groups[cache.group]
+        q = proj[:, :self.q_size]
+        if cache.write:
+            ops.paged_write(proj[:, self.q_size:self.q_size + self.k_size], cache.k_pages, gv.slot_mapping)
+            ops.paged_write(proj[:, self.q_size + self.k_size:], cache.v_pages, gv.slot_mapping)
+        ops.biased_attention(q, cache.k_pages, cache.v_pages, gv.block_table, ctx, out, num_heads=self.num_heads,
+                             num_kv_heads=self.num_kv_heads, scale=self.scale, dist_bias=self.dist_bias,
+                             q_scale=self.q_scale, out_scale=out_scale, window=self.window)
+
+
+register_part("mixer", "distance_bias_attention", DistanceBiasAttention)

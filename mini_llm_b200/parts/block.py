@@ -2,6 +2,7 @@
 
 "pre_norm" is the reference's block (src/model/gpt2_model.cu:271-365):
 x += mixer(norm(x)); x += ff(norm(x)), with the residual stream x in 32-bit.
+"parallel": x += mixer(norm_a(x)) + ff(norm_b(x)), both branches reading the same x.
 """
 from __future__ import annotations
 
@@ -17,8 +18,31 @@ def _norm(norm, consumer, x, ctx):
 
 def pre_norm(layer, x, ctx, cache):
     layer.mixer.forward(_norm(layer.mixer_norm, layer.mixer, x, ctx), ctx, cache, x)
-    layer.ff.forward(_norm(layer.ff_norm, layer.ff, x, ctx), ctx, x)
+    if layer.ff is not None:
+        layer.ff.forward(_norm(layer.ff_norm, layer.ff, x, ctx), ctx, x)
     return x
 
 
 register_part("arrangement", "pre_norm", lambda: pre_norm)
+
+
+def parallel(layer, x, ctx, cache):
+    """x += mixer(norm_a(x)) + ff(norm_b(x)): both norms read the same x, so both are taken before
+    either result is added; two RMS norms that differ only in their weights share one kernel."""
+    if layer.ff is None:
+        layer.mixer.forward(layer.mixer_norm.forward(x, ctx), ctx, cache, x)
+        return x
+    pair = getattr(layer.mixer_norm, "pairs_with", None)
+    if pair is not None and pair(layer.ff_norm):
+        h1, h2 = layer.mixer_norm.forward_pair(layer.ff_norm, x, ctx)
+    else:
+        h1 = layer.mixer_norm.forward(x, ctx)
+        h2 = layer.ff_norm.forward(x, ctx)
+        if h2.data_ptr() == h1.data_ptr():
+            raise RuntimeError("parallel arrangement: the two norms wrote to the same buffer")
+    layer.mixer.forward(h1, ctx, cache, x)
+    layer.ff.forward(h2, ctx, x)
+    return x
+
+
+register_part("arrangement", "parallel", lambda: parallel)

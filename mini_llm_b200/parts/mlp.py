@@ -41,3 +41,44 @@ class MLP(FeedForward):
 
 
 register_part("feed_forward", "mlp", MLP)
+
+
+GATE_ACTIVATIONS = ("relu", "silu", "gelu_tanh", "gelu_erf")
+
+
+class GatedMLP(FeedForward):
+    """x += W_down (act(W_gate h) * (W_up h)), no biases.  The gate and the up matrix are stacked into one
+    [2F, D] matrix when the weights are bound, so both come from one product; a small kernel applies the
+    activation and multiplies the halves; the down-projection adds into the residual in its epilogue."""
+
+    def __init__(self, hidden_size: int, inner_size: int, activation: str = "silu"):
+        if activation not in GATE_ACTIVATIONS:
+            raise ValueError(f"GatedMLP activation must be one of {GATE_ACTIVATIONS}, got {activation!r}")
+        self.hidden_size = int(hidden_size)
+        self.inner_size = int(inner_size)
+        self.activation = activation
+
+    def param_specs(self):
+        return {"gate_weight": ParamSpec((self.inner_size, self.hidden_size), "matrix"),
+                "up_weight": ParamSpec((self.inner_size, self.hidden_size), "matrix"),
+                "down_weight": ParamSpec((self.hidden_size, self.inner_size), "matrix")}
+
+    def bind(self, params, rt) -> None:
+        import torch
+        super().bind(params, rt)
+        if "gate_weight" in params:
+            self.gate_up_weight = torch.cat([self.gate_weight, self.up_weight], 0).contiguous()
+            self.gate_weight = self.gate_up_weight[:self.inner_size]
+            self.up_weight = self.gate_up_weight[self.inner_size:]
+
+    def forward(self, h, ctx, out_accum):
+        ops = self.rt.ops
+        T, F = h.shape[0], self.inner_size
+        gu = ctx.ws.buf("ff_gate_up", T, 2 * F, self.rt.act_dtype)
+        ops.linear(h, self.gate_up_weight, None, out=gu)
+        mid = ctx.ws.buf("ff_mid", T, F, self.rt.act_dtype)
+        ops.gated_act(gu, mid, self.activation)
+        ops.linear(mid, self.down_weight, None, out=out_accum, accumulate=True)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

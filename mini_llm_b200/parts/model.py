@@ -38,8 +38,8 @@ class Layer:
         self.spec = spec
         self.mixer_norm = build_part("norm", spec.mixer_norm)
         self.mixer = build_part("mixer", spec.mixer)
-        self.ff_norm = build_part("norm", spec.ff_norm)
-        self.ff = build_part("feed_forward", spec.ff)
+        self.ff_norm = build_part("norm", spec.ff_norm) if spec.ff is not None else None
+        self.ff = build_part("feed_forward", spec.ff) if spec.ff is not None else None
         self.arrangement = get_part_factory("arrangement", spec.arrangement)()
 
 
@@ -73,7 +73,13 @@ class Model:
         return getattr(self, label)
 
     def layer_needs(self) -> Dict[int, object]:
-        return {i: l.mixer.cache_need() for i, l in enumerate(self.layers)}
+        """Cache unit -> what it must hold: every layer's own unit, and one more for every run of the
+        schedule that keeps a cache of its own."""
+        needs = {i: l.mixer.cache_need() for i, l in enumerate(self.layers)}
+        for e in self.spec.schedule:
+            if e.private_cache:
+                needs[e.cache_unit] = self.layers[e.layer].mixer.cache_need()
+        return needs
 
     def finish_binding(self, rt) -> None:
         """Called once all parts have their parameters."""
@@ -82,17 +88,19 @@ class Model:
             self.head.tie(self.embedding)
 
     def layer_cache(self, cache_manager, entry) -> LayerCache:
-        owner = entry.cache_of
-        write = owner == entry.layer
-        need = self.layers[owner].mixer.cache_need()
-        if isinstance(need, PagedNeed):
-            gi = cache_manager.group_of_layer[owner]
-            g = cache_manager.groups[gi]
-            li = g.layer_index(owner)
-            return LayerCache(group=gi, k_pages=g.pool[li, 0], v_pages=g.pool[li, 1], write=write)
-        if isinstance(need, StateNeed):
-            return LayerCache(state=cache_manager.states[owner], write=write)
-        return LayerCache(write=write)
+        owner = entry.cache_unit
+        write = entry.private_cache or entry.cache_of == entry.layer
+        need = self.layers[entry.cache_of].mixer.cache_need()
+        out = LayerCache(write=write)
+        for nd in (need if isinstance(need, (list, tuple)) else (need,)):     # a mixer of several branches may need both kinds
+            if isinstance(nd, PagedNeed):
+                gi = cache_manager.group_of_layer[owner]
+                g = cache_manager.groups[gi]
+                li = g.layer_index(owner)
+                out.group, out.k_pages, out.v_pages = gi, g.k_pages(li), g.v_pages(li)
+            elif isinstance(nd, StateNeed):
+                out.state = cache_manager.states[owner]
+        return out
 
     def prepare(self, cache_manager) -> None:
         self._caches = [self.layer_cache(cache_manager, e) for e in self.spec.schedule]

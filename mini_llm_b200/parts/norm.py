@@ -33,3 +33,37 @@ class LayerNorm(Norm):
 
 
 register_part("norm", "layernorm", LayerNorm)
+
+
+class RMSNorm(Norm):
+    """y = x / sqrt(mean(x^2) + eps) * (w + 1) for weights stored around zero (``unit_offset``), or * w for
+    plain weights; eps inside the root, all 32-bit.  ``forward_pair`` norms the same rows with two weight
+    vectors (this norm's and ``other``'s) from one sum of squares: the two branches of a parallel block."""
+
+    def __init__(self, hidden_size: int, eps: float, unit_offset: bool = False):
+        self.hidden_size = int(hidden_size)
+        self.eps = float(eps)
+        self.unit_offset = bool(unit_offset)
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.hidden_size,), "vector")}
+
+    def forward(self, x, ctx, rows=None, lazy=False, name="norm_out"):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.ws.buf(name, n, self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows=rows, unit_offset=self.unit_offset)
+        return out
+
+    def pairs_with(self, other) -> bool:
+        return (isinstance(other, RMSNorm) and other.hidden_size == self.hidden_size and other.eps == self.eps
+                and other.unit_offset == self.unit_offset)
+
+    def forward_pair(self, other, x, ctx):
+        n = x.shape[0]
+        out1 = ctx.ws.buf("norm_out", n, self.hidden_size, self.rt.act_dtype)
+        out2 = ctx.ws.buf("norm_out_b", n, self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.rmsnorm(x, self.weight, self.eps, out1, unit_offset=self.unit_offset, weight2=other.weight, out2=out2)
+        return out1, out2
+
+
+register_part("norm", "rmsnorm", RMSNorm)

@@ -50,13 +50,14 @@ class LayerSpec:
     """One block: a mixer and a feed-forward, each behind its norm.
 
     ``arrangement`` names how they are wired (registry ``ARRANGEMENTS``), e.g.
-    "pre_norm": x += mixer(norm(x)); x += ff(norm(x)).
+    "pre_norm": x += mixer(norm(x)); x += ff(norm(x)); "parallel": both read the
+    same x.  ``ff`` and ``ff_norm`` are None for a layer without a feed-forward.
     """
 
     mixer: PartSpec
-    ff: PartSpec
+    ff: Optional[PartSpec]
     mixer_norm: PartSpec
-    ff_norm: PartSpec
+    ff_norm: Optional[PartSpec]
     arrangement: str = "pre_norm"
 
 
@@ -64,14 +65,23 @@ class LayerSpec:
 class ScheduleEntry:
     """One run of a layer.  ``cache_of``: the layer whose cache (pages or state)
     this run uses; when it differs from ``layer`` the run only reads that cache
-    and writes nothing to it."""
+    and writes nothing to it.  ``private_cache``: the run has a cache and a state
+    of its own (of the kind its layer's mixer needs) that no other run touches:
+    a layer that runs several times with the same weights, each run with its own
+    history.  ``cache_unit`` (set by ModelSpec) is the id under which the cache
+    manager keeps the run's cache: the layer's index, or a number beyond the
+    layers for a private one."""
 
     layer: int
     cache_of: Optional[int] = None
+    private_cache: bool = False
+    cache_unit: Optional[int] = None
 
     def __post_init__(self):
         if self.cache_of is None:
             self.cache_of = self.layer
+        if self.private_cache and self.cache_of != self.layer:
+            raise ValueError("a run with a private cache cannot also borrow another layer's")
 
 
 @dataclass
@@ -92,9 +102,15 @@ class ModelSpec:
         if self.schedule is None:
             self.schedule = [ScheduleEntry(i) for i in range(len(self.layers))]
         n = len(self.layers)
+        private = 0
         for e in self.schedule:
             if not (0 <= e.layer < n) or not (0 <= e.cache_of < n):
                 raise ValueError(f"schedule entry {e} names a layer outside 0..{n - 1}")
+            if e.private_cache:
+                e.cache_unit = n + private
+                private += 1
+            else:
+                e.cache_unit = e.cache_of
 
     def all_part_specs(self):
         """(label, PartSpec) of every part, in a fixed order."""
@@ -103,7 +119,8 @@ class ModelSpec:
         for i, l in enumerate(self.layers):
             yield f"layers.{i}.mixer_norm", l.mixer_norm
             yield f"layers.{i}.mixer", l.mixer
-            yield f"layers.{i}.ff_norm", l.ff_norm
-            yield f"layers.{i}.ff", l.ff
+            if l.ff is not None:
+                yield f"layers.{i}.ff_norm", l.ff_norm
+                yield f"layers.{i}.ff", l.ff
         yield "final_norm", self.final_norm
         yield "head", self.head

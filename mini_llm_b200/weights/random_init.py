@@ -3,7 +3,7 @@
 The folder holds config.json and model.safetensors with the architecture's own
 tensor names and layouts, so it loads like any checkpoint.  Rules come from
 the model description's ``WeightRef.init``: N(0, std) matrices and tables,
-ones / zeros for norm weights and biases.  Values are drawn on the CPU in
+ones / zeros for norm weights and biases, U(a, b) where a rule says so.  Values are drawn on the CPU in
 32-bit from one seeded generator, tensor by tensor in the description's order,
 then stored in ``dtype``.  (The reference has no such mode: it needs the real
 checkpoint exported by scripts/export_weights.py.)
@@ -35,6 +35,8 @@ def random_tensors(spec, model, seed: int, dtype: torch.dtype = torch.float32):
             kind = ref.init[0]
             if kind == "normal":
                 t = torch.empty(shape, dtype=torch.float32).normal_(0.0, float(ref.init[1]), generator=gen)
+            elif kind == "uniform":
+                t = torch.empty(shape, dtype=torch.float32).uniform_(float(ref.init[1]), float(ref.init[2]), generator=gen)
             elif kind == "ones":
                 t = torch.ones(shape, dtype=torch.float32)
             elif kind == "zeros":
