@@ -105,7 +105,8 @@ class Replay:
         self.p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
         self.n = 0
         with open(os.path.join(model_dir, "config.json")) as f:
-            self.vocab = json.load(f)["vocab_size"]
+            cfg = json.load(f)
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
 
     def step(self, entries, end=()):
         """entries: list of (id, tokens, want).  Returns [wanted, vocab] float32 or None."""

@@ -47,9 +47,10 @@ def distance_bias(n_q: int, n_k: int, q_start: int, r1, r2):
     return r1[:, None, None] * torch.log1p(r2[:, None, None] * dist[None])
 
 
-def softmax_branch(h, w: Dict[str, torch.Tensor], c: dict, store: Callable = _keep):
+def softmax_branch(h, w: Dict[str, torch.Tensor], c: dict, store: Callable = _keep, out_scale: float = 1.0):
     """Causal softmax attention with grouped key/value heads, a query temperature that grows with the
-    position and a logarithmic distance penalty.  h [T, D] -> [T, D]."""
+    position and a logarithmic distance penalty.  h [T, D] -> [T, D], times out_scale (the engine applies a
+    branch's factor to the attention's result before it rounds it for the output projection; so does this)."""
     T = h.shape[0]
     H, G, dk, dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
     q = store(h @ w["q"].t()).view(T, H, dk)
@@ -67,7 +68,7 @@ def softmax_branch(h, w: Dict[str, torch.Tensor], c: dict, store: Callable = _ke
         s = (q[:, hh] @ k[:, g].t()) * float(c["scale"]) - bias[hh]
         s = s.masked_fill(~mask, float("-inf"))
         out[:, hh] = torch.softmax(s, -1) @ v[:, g]
-    return store(out.reshape(T, H * dv)) @ w["o"].t()
+    return store(out_scale * out.reshape(T, H * dv)) @ w["o"].t()
 
 
 def forget_gate(z, bias, lower):
@@ -88,17 +89,18 @@ def gated_recurrence(q, f, v, state: Optional[torch.Tensor] = None):
     return o, S
 
 
-def recurrent_branch(h, w: Dict[str, torch.Tensor], c: dict, eps: float, store: Callable = _keep):
-    """The gated linear-attention branch whose forget gate also sets what is written.  h [T, D] -> [T, D]."""
+def recurrent_branch(h, w: Dict[str, torch.Tensor], c: dict, eps: float, store: Callable = _keep, out_scale: float = 1.0):
+    """The gated linear-attention branch whose forget gate also sets what is written.  h [T, D] -> [T, D], times
+    out_scale (applied where the engine applies it: to the normed outputs, before they are rounded)."""
     T = h.shape[0]
     Hr, ek, ev = c["heads"], c["dim"], c["vdim"]
-    q = store(torch.nn.functional.silu(store(h @ w["q"].t()))).view(T, Hr, ek)
+    q = torch.nn.functional.silu(store(h @ w["q"].t())).view(T, Hr, ek)
     z = store(h @ w["f"].t())
     f = forget_gate(z, w["f.b"].to(F64), w["lower"].to(F64)).view(T, Hr, ek)
     v = store(h @ w["v"].t()).view(T, Hr, ev)
     o, _ = gated_recurrence(q, f, v)
     o = rms_norm(o, w["norm"].to(F64), eps, unit_offset=False)
-    return store(o.reshape(T, Hr * ev)) @ w["o"].t()
+    return store(out_scale * o.reshape(T, Hr * ev)) @ w["o"].t()
 
 
 def dense_ff(h, w: Dict[str, torch.Tensor], store: Callable = _keep):
@@ -136,9 +138,8 @@ def forward(tensors: Dict[str, torch.Tensor], cfg: dict, ids: List[int], store: 
         p = f"l{weight_layer(cfg, i)}."
         m = layer["mixer"]
         h1 = store(rms_norm(x, tensors[p + "norm1"].to(F64), eps, unit_offset=True))
-        left = softmax_branch(h1, _sub(tensors, p + "mix.left."), m["left"], store)
-        right = recurrent_branch(h1, _sub(tensors, p + "mix.right."), m["right"], eps, store)
-        add = float(m["left_scale"]) * left + float(m["right_scale"]) * right
+        add = softmax_branch(h1, _sub(tensors, p + "mix.left."), m["left"], store, float(m["left_scale"])) \
+            + recurrent_branch(h1, _sub(tensors, p + "mix.right."), m["right"], eps, store, float(m["right_scale"]))
         if layer.get("mlp"):
             if layer["mlp"]["kind"] != "dense":
                 raise ValueError(f"layer {i}: unknown feed-forward kind {layer['mlp']['kind']!r}")
