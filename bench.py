@@ -40,6 +40,9 @@ with "impl": "reference" and "dtype": "fp32".  The reference holds at most 16 re
 (more are cut) and there is no batch-64 point.  Where it cannot be built or run the line is
 {"impl": "reference", "unavailable": "<why>"}.
 
+``--compare-designs [small,medium,large]`` measures the engine's other design, Finuvik, beside GPT-2 at equal
+width, depth, head count and head size (bfloat16 unless --dtype is given).
+
 ``--profile-step prefill|decode [--kernel-times]`` runs one small eager step (for a profiler, or to
 print each kernel's share of the step from CUDA events); ``--workload medium|xl`` runs the
 continuous-batching workloads of the larger GPT-2 sizes.
@@ -412,6 +415,158 @@ def run_workload(kind: str, dtype: str, layers: int) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --compare-designs: Finuvik beside GPT-2 at equal width, depth, head count and head size (random weights)
+DESIGN_SIZES = {
+    # name: width, layers, heads, key/value heads of Finuvik's softmax branch, GPT-2 inner size, Finuvik inner size
+    "small": dict(width=768, layers=4, heads=12, kv_heads=4, inner=3072, gated_inner=2048),
+    "medium": dict(width=1024, layers=4, heads=16, kv_heads=4, inner=4096, gated_inner=2752),
+    "large": dict(width=2048, layers=2, heads=16, kv_heads=4, inner=8192, gated_inner=5504),
+}
+DESIGN_VOCAB, DESIGN_POSITIONS = 32000, 1024
+
+
+def design_configs(size: str):
+    z = DESIGN_SIZES[size]
+    D, H, L = z["width"], z["heads"], z["layers"]
+    dh = D // H
+    gpt2 = dict(SMALL, n_layer=L, n_embd=D, n_head=H, n_inner=z["inner"], vocab_size=DESIGN_VOCAB,
+                n_positions=DESIGN_POSITIONS, eos_token_id=DESIGN_VOCAB - 1, tie_word_embeddings=False)
+    # the softmax branch has GPT-2's heads (grouped keys and values, values as wide as keys); the recurrent branch has
+    # a quarter as many heads with states of dh/2 x 2dh, i.e. half of the width in value channels
+    layer = dict(type="parallel",
+                 mixer=dict(left=dict(heads=H, kv_heads=z["kv_heads"], dim=dh, vdim=dh, scale=dh ** -0.5,
+                                      q_temp=dict(coef=0.1, every=256)),
+                            left_scale=1.0, right=dict(heads=max(1, H // 4), dim=dh // 2, vdim=2 * dh), right_scale=1.0),
+                 mlp=dict(ff=z["gated_inner"], kind="dense"))
+    finuvik = dict(architecture="Finuvik", width=D, vocab=DESIGN_VOCAB, max_positions=DESIGN_POSITIONS,
+                   norm=dict(eps=1e-5), layers=[dict(layer) for _ in range(L)])
+    return {"gpt2": gpt2, "finuvik": finuvik}
+
+
+def _design_model(model_dir, dtype, batch, tokens):
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner
+    return ModelRunner(model_dir, EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=tokens, max_num_seqs=batch,
+                                               max_num_batched_tokens=max(2048, batch)))
+
+
+def _kernel_rows(tl):
+    rows = tl.rows()
+    return {name.replace("mllm_", ""): {"launches": k, "us": round(ms * 1e3, 1)} for name, k, ms in rows}
+
+
+def design_prefill(model_dir, dtype, iters=5, warmup=3):
+    """2 x 1024 prompt tokens in one step from a cold L2: median milliseconds; then the same step once more with every
+    launch timed (eager launches)."""
+    import torch
+    from mini_llm_b200 import ops
+    from mini_llm_b200.engine.runner import StepEntry
+    n, B = DESIGN_POSITIONS, PREFILL_TOKENS // DESIGN_POSITIONS
+    runner = _design_model(model_dir, dtype, B, PREFILL_TOKENS)
+    g = torch.Generator().manual_seed(99)
+    prompts = [torch.randint(0, DESIGN_VOCAB, (n,), generator=g).to(torch.int32).numpy() for _ in range(B)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=runner.device)
+    times, kernels = [], None
+    for it in range(warmup + iters + 1):
+        for i in range(B):
+            runner.add_request(i)
+        flush.zero_()                                    # larger than L2: the step starts cold
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if it == warmup + iters:
+            runner.engine.use_cuda_graphs = False
+            with ops.time_launches() as tl:
+                runner.step([StepEntry(i, prompts[i], [n - 1]) for i in range(B)])
+            kernels = _kernel_rows(tl)
+        else:
+            e0.record()
+            runner.step([StepEntry(i, prompts[i], [n - 1]) for i in range(B)])
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(e0.elapsed_time(e1))
+        for i in range(B):
+            runner.finish_request(i)
+    ops.check_device_errors()
+    ms = sorted(times)[len(times) // 2]
+    del runner
+    torch.cuda.empty_cache()
+    return dict(ms=round(ms, 3), tok_s=round(PREFILL_TOKENS / (ms / 1e3), 1), kernels=kernels)
+
+
+def design_decode(model_dir, dtype, batch, steps):
+    """``steps`` decode steps (forward + argmax) of ``batch`` requests after 512-token prompts, device-timed, after the
+    same generation by other requests (so the timed steps replay captured graphs); then one eager step with every
+    launch timed."""
+    import torch
+    from mini_llm_b200 import ops
+    from mini_llm_b200.engine.runner import StepEntry
+    runner = _design_model(model_dir, dtype, batch, batch * DESIGN_POSITIONS)
+    prompts = bench_prompts(DESIGN_VOCAB, batch)
+    out = torch.empty(batch, dtype=torch.int32, device=runner.device)
+
+    def start(tag):
+        ids = [(tag, i) for i in range(batch)]
+        for r in ids:
+            runner.add_request(r)
+        for lo in range(0, batch, 4):
+            runner.step([StepEntry(ids[i], prompts[i], []) for i in range(lo, min(batch, lo + 4))])
+        return ids
+
+    def one(ids):
+        ops.argmax(runner.step([StepEntry(r, [11], [0]) for r in ids]), out)
+
+    ids = start("warm")
+    for _ in range(steps):
+        one(ids)
+    for r in ids:
+        runner.finish_request(r)
+    ids = start("timed")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    n0 = ops.launches
+    e0.record()
+    for _ in range(steps):
+        one(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = (ops.launches - n0) // steps
+    runner.engine.use_cuda_graphs = False
+    with ops.time_launches() as tl:
+        one(ids)
+    kernels = _kernel_rows(tl)
+    ops.check_device_errors()
+    ctx = runner.computed(ids[0])
+    del runner
+    torch.cuda.empty_cache()
+    return dict(ms_per_step=round(ms, 4), tok_s=round(batch / (ms / 1e3), 1), launches_per_step=launches, context=ctx,
+                kernels=kernels)
+
+
+def run_compare_designs(sizes, dtype: str, batch: int, steps: int) -> int:
+    """Prefill and decode throughput of Finuvik beside GPT-2 (the closest model of the engine) at equal width, depth,
+    head count and head size, random weights; one JSON line per size.  Per kernel entry point the line carries the
+    microseconds of one eager step, from which the rooflines of the like kernels are compared."""
+    import torch
+    import mini_llm_b200 as m
+    pk = peaks()
+    steps = max(3, min(steps, DESIGN_POSITIONS - PROMPT_LEN - 2))
+    for size in sizes:
+        line = {"compare_designs": size, "dtype": dtype, "batch": batch, "decode_steps": steps,
+                "sizes": DESIGN_SIZES[size], "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]}}
+        for name, cfg in design_configs(size).items():
+            with tempfile.TemporaryDirectory(prefix="mini_llm_cmp_") as d:
+                m.write_random_model(cfg, 0, d, dtype=dtype)
+                pf = design_prefill(d, dtype)
+                dc = design_decode(d, dtype, batch, steps)
+                params = sum(os.path.getsize(os.path.join(d, f)) for f in os.listdir(d) if f.endswith(".safetensors"))
+            line[name] = {"weight_bytes": params, "prefill": pf, "decode": dc}
+        print(json.dumps(line), flush=True)
+    return 0
+
+
 def fp32_peak_flops() -> float:
     """CUDA-core peak of the float32 path (no tensor-core mode exists for true 32-bit products):
     SMs x 128 lanes x 2 flops x the highest SM clock; nominal, nothing measures it on this pool."""
@@ -553,7 +708,18 @@ def main() -> int:
                     help="mma_sync: prompt portions stay on the mma.sync attention kernel (to compare or profile it)")
     ap.add_argument("--workload", choices=["medium", "xl"],
                     help="run a continuous-batching workload of GPT-2 medium or XL instead of the benchmark")
+    ap.add_argument("--compare-designs", nargs="?", const="small,medium,large", metavar="SIZES",
+                    help="measure Finuvik beside GPT-2 at equal sizes (a comma list of small, medium, large) instead of "
+                         "the benchmark: prefill of 2 x 1024 tokens and decode at --batch, one JSON line per size")
     args = ap.parse_args()
+    if args.compare_designs:
+        sizes = [z for z in args.compare_designs.split(",") if z]
+        bad = [z for z in sizes if z not in DESIGN_SIZES]
+        if bad:
+            print(f"bench.py: unknown size(s) {bad}; known: {sorted(DESIGN_SIZES)}")
+            return 2
+        return run_compare_designs(sizes, "bfloat16" if args.dtype == "float32" and "--dtype" not in sys.argv else args.dtype,
+                                   args.batch, min(args.steps, 128))
     if args.attention == "mma_sync":
         from mini_llm_b200 import ops
         ops.use_tcgen05_attention = False

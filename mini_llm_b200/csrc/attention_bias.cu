@@ -12,8 +12,8 @@
 // others.  `tiled`: 64 queries x 32 keys per CTA and head for prompt portions: queries in shared memory, a key
 // tile staged transposed and a value tile as it is, 2 x 4 scores and 2 x dv/8 outputs per thread.  `split`: single
 // tokens (decode): the keys of a token are cut into splits of 256 starting at multiples of 256 from position 0, a
-// CTA of four warps takes one (token, head, split), the partial (o, m, l) of the splits are merged in split order
-// by a second kernel.  Key chunks and tiles start at multiples of 32 from position 0 in all three, so a token's
+// CTA takes one split for up to four query heads that share a key/value head (rows staged once in shared memory),
+// the partial (o, m, l) of the splits are merged in split order by a second kernel.  Key chunks and tiles start at multiples of 32 from position 0 in all three, so a token's
 // sums run in an order that depends on its position only, not on how the step was cut or batched.
 #include "common.cuh"
 
@@ -131,71 +131,177 @@ attention_bias_simt_kernel(const T* q, long long q_stride, const T* k_pages, con
 }
 
 // ------------------------------------------------------------------------------------------------ decode
-constexpr int SPLIT = 256;          // keys per split; a CTA's four warps take 64 each
+constexpr int SPLIT = 256;          // keys per split
 
-// grid (splits, H, T).  Partial results: part_o [T][H][splits][dv], part_ml [T][H][splits][2]; a split that lies
-// beyond the token's keys (or before its window) writes l = 0.
+// Single tokens.  grid (splits, kv heads x head chunks, tokens).  A CTA takes one split of one token's keys for HG
+// (1, 2 or 4) query heads that share a key/value head, so a key or value row is fetched once for all of them.  The
+// split is walked in tiles of 32 * KS keys (KS = 4 / HG key sub-tiles) that are staged in shared memory with 16-byte
+// loads (all loads of a burst before any store); warp w takes head w % HG and sub-tile w / HG: its lanes are the 32
+// keys for the scores (a row of K per lane, the query broadcast) and 32 value columns at a time for the weighted sum.
+// Sub-tile k of tile i covers the absolute positions [split*256 + (i*KS + k)*32, +32): chunks of 32 from position 0.
+// Partial results: part_o [T][H][splits][dv], part_ml [T][H][splits][2]; a split without visible keys writes l = 0.
 template <typename T>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(128)
 attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, const T* v_pages,
                             const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int H, int Hkv, int dk, int dv, int page_size, BiasArgs a) {
-    __shared__ float qs[MAX_D];
-    __shared__ float so[WARPS][MAX_D];
-    __shared__ float sml[WARPS][2];
+                            int H, int Hkv, int dk, int dv, int page_size, int HG, int KS, BiasArgs a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int VEC = 16 / sizeof(T);
+    const int krow = dk + VEC;                                  // elements per staged key row: 16 bytes of padding
+    const int tile = 32 * KS;
+    T* Ks = reinterpret_cast<T*>(smraw);                        // [tile][dk + VEC]
+    T* Vs = Ks + (size_t)tile * krow;                           // [tile][dv]
+    float* qs = reinterpret_cast<float*>(Vs + (((size_t)tile * dv + VEC - 1) / VEC) * VEC);   // [HG][dk]
+    float* so = qs + HG * dk;                                   // [warps][dv] at the end
+    float* sml = so + 4 * dv;                                   // [warps][2]
     pdl_wait();
     pdl_launch();
-    const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, t = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hk = h / (H / Hkv);
+    const int split = blockIdx.x, nsplit = gridDim.x, t = blockIdx.z;
+    const int R = H / Hkv, chunks = (R + HG - 1) / HG;
+    const int hk = blockIdx.y / chunks, h0 = hk * R + (blockIdx.y % chunks) * HG;
+    const int nh = min(HG, hk * R + R - h0);                    // heads this CTA really has
+    const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+    const int wh = warp % HG, wk = warp / HG;                   // this warp's head and key sub-tile
+    const int h = h0 + wh;
+    const bool live = wh < nh;
     const int seq = token_seq[t], p = positions[t];
-    const size_t pidx = ((size_t)t * H + h) * nsplit + split;
     int first = 0;
     if (a.window > 0 && p - a.window + 1 > 0) first = p - a.window + 1;
     const int s_lo = max(first, split * SPLIT), s_hi = min(p, split * SPLIT + SPLIT - 1);
-    if (s_lo > s_hi) {                                   // uniform over the CTA
-        if (threadIdx.x == 0) { part_ml[pidx * 2] = -INFINITY; part_ml[pidx * 2 + 1] = 0.f; }
+    if (s_lo > s_hi) {                                          // uniform over the CTA
+        if (tid < nh) { const size_t pi = ((size_t)t * H + h0 + tid) * nsplit + split; part_ml[pi * 2] = -INFINITY; part_ml[pi * 2 + 1] = 0.f; }
         return;
     }
     const int* bt = block_table + (size_t)seq * bt_stride;
-    const T* qrow = q + (size_t)t * q_stride + (size_t)h * dk;
-    for (int d = threadIdx.x; d < dk; d += WARPS * 32) qs[d] = to_f32(qrow[d]);
-    __syncthreads();
+    for (int i = tid; i < HG * dk; i += nthreads) {
+        const int hh = i / dk, d = i % dk;
+        qs[i] = hh < nh ? to_f32(q[(size_t)t * q_stride + (size_t)(h0 + hh) * dk + d]) : 0.f;
+    }
     const float qf = a.scale * (a.q_scale ? a.q_scale[p] : 1.0f);
+    const float* brow = (a.dist_bias && live) ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
     constexpr int NACC = MAX_D / 32;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const int w_lo = max(s_lo, split * SPLIT + warp * (SPLIT / WARPS));
-    const int w_hi = min(s_hi, split * SPLIT + (warp + 1) * (SPLIT / WARPS) - 1);
-    if (w_lo <= w_hi)
-        warp_walk<T>(qs, k_pages, v_pages, bt, p, h, hk, Hkv, dk, dv, page_size, w_lo, w_hi, a, qf, acc, m, l);
+    const int kpieces = dk / VEC;
+    const int vpieces = (dv % VEC == 0 && ((uintptr_t)v_pages % 16) == 0) ? dv / VEC : 0;   // 0: value rows are copied by element
+
+    for (int base = (s_lo / tile) * tile; base <= s_hi; base += tile) {
+        __syncthreads();                                        // the tile before is no longer read; qs is complete
+        constexpr int LD = 4;
+        for (int i0 = tid; i0 < tile * kpieces; i0 += nthreads * LD) {
+            uint4 r[LD];
+#pragma unroll
+            for (int u = 0; u < LD; ++u) {
+                const int i = i0 + u * nthreads, key = i / kpieces, piece = i % kpieces, kp = base + key;
+                r[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < tile * kpieces && kp >= s_lo && kp <= s_hi)
+                    r[u] = *reinterpret_cast<const uint4*>(k_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dk + piece * VEC);
+            }
+#pragma unroll
+            for (int u = 0; u < LD; ++u) {
+                const int i = i0 + u * nthreads;
+                if (i < tile * kpieces) *reinterpret_cast<uint4*>(Ks + (size_t)(i / kpieces) * krow + (i % kpieces) * VEC) = r[u];
+            }
+        }
+        if (vpieces) {
+            for (int i0 = tid; i0 < tile * vpieces; i0 += nthreads * LD) {
+                uint4 r[LD];
+#pragma unroll
+                for (int u = 0; u < LD; ++u) {
+                    const int i = i0 + u * nthreads, key = i / vpieces, piece = i % vpieces, kp = base + key;
+                    r[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (i < tile * vpieces && kp >= s_lo && kp <= s_hi)
+                        r[u] = *reinterpret_cast<const uint4*>(v_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dv + piece * VEC);
+                }
+#pragma unroll
+                for (int u = 0; u < LD; ++u) {
+                    const int i = i0 + u * nthreads;
+                    if (i < tile * vpieces) *reinterpret_cast<uint4*>(Vs + (size_t)(i / vpieces) * dv + (i % vpieces) * VEC) = r[u];
+                }
+            }
+        } else {
+            for (int i = tid; i < tile * dv; i += nthreads) {
+                const int key = i / dv, d = i % dv, kp = base + key;
+                T val = from_f32<T>(0.f);
+                if (kp >= s_lo && kp <= s_hi)
+                    val = v_pages[(((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dv + d];
+                Vs[(size_t)key * dv + d] = val;
+            }
+        }
+        __syncthreads();
+        const int c0 = base + wk * 32;                          // this warp's 32 keys
+        if (!live || c0 > s_hi || c0 + 31 < s_lo) continue;     // uniform over the warp (barriers are outside)
+        const int kp = c0 + lane;
+        const bool valid = kp >= s_lo && kp <= s_hi;
+        const T* kr = Ks + (size_t)(wk * 32 + lane) * krow;
+        const float* qh = qs + wh * dk;
+        float dot = 0.f;
+        for (int d = 0; d < dk; d += VEC) {
+            float kv[8];
+            if constexpr (sizeof(T) == 4) {
+                const float4 x = *reinterpret_cast<const float4*>(kr + d);
+                kv[0] = x.x; kv[1] = x.y; kv[2] = x.z; kv[3] = x.w;
+            } else {
+                load8(kr + d, kv);
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) dot = fmaf(qh[d + e], kv[e], dot);
+        }
+        float sc = -INFINITY;
+        if (valid) {
+            sc = dot * qf;
+            if (brow) sc += brow[p - kp];
+        }
+        const float m_new = fmaxf(m, warp_max(sc));             // at least one key of the chunk is visible
+        const float alpha = expf(m - m_new);
+        const float pr = valid ? expf(sc - m_new) : 0.f;
+        l = l * alpha + warp_sum(pr);
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
+        const T* vt = Vs + (size_t)(wk * 32) * dv;
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < dv) acc[i] = fmaf(pj, to_f32(vt[(size_t)j * dv + d]), acc[i]);
+            }
+        }
+    }
+    __syncthreads();
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < dv) so[warp][d] = acc[i];
+        if (d < dv) so[warp * dv + d] = acc[i];
     }
-    if (lane == 0) { sml[warp][0] = m; sml[warp][1] = l; }
+    if (lane == 0) { sml[warp * 2] = m; sml[warp * 2 + 1] = l; }
     __syncthreads();
-    // the four warps' states meet in warp order
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, sml[w][0]);
-    float f[WARPS], ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-        f[w] = sml[w][1] > 0.f ? expf(sml[w][0] - mm) : 0.f;
-        ll += sml[w][1] * f[w];
+    // the key sub-tiles of a head meet in sub-tile order
+    for (int hh = 0; hh < nh; ++hh) {
+        float mm = -INFINITY;
+        for (int k = 0; k < KS; ++k)
+            if (sml[(k * HG + hh) * 2 + 1] > 0.f) mm = fmaxf(mm, sml[(k * HG + hh) * 2]);
+        float ll = 0.f;
+        for (int k = 0; k < KS; ++k) {
+            const float lw = sml[(k * HG + hh) * 2 + 1];
+            if (lw > 0.f) ll += lw * expf(sml[(k * HG + hh) * 2] - mm);
+        }
+        const size_t pi = ((size_t)t * H + h0 + hh) * nsplit + split;
+        for (int d = tid; d < dv; d += nthreads) {
+            float o = 0.f;
+            for (int k = 0; k < KS; ++k) {
+                const float lw = sml[(k * HG + hh) * 2 + 1];
+                if (lw > 0.f) o += so[(k * HG + hh) * dv + d] * expf(sml[(k * HG + hh) * 2] - mm);
+            }
+            part_o[pi * dv + d] = o;
+        }
+        if (tid == 0) { part_ml[pi * 2] = mm; part_ml[pi * 2 + 1] = ll; }
     }
-    for (int d = threadIdx.x; d < dv; d += WARPS * 32) {
-        float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) o += so[w][d] * f[w];
-        part_o[pidx * dv + d] = o;
-    }
-    if (threadIdx.x == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = ll; }
 }
 
 // One warp per (token, head): out = out_scale * sum_s o_s e^(m_s - m) / sum_s l_s e^(m_s - m), in split order.
@@ -464,18 +570,31 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
     }
     if (impl == 2) {
         if (!part_o || !part_ml || nsplit <= 0) return mllm_fail(1, "attention_bias: the split kernel needs scratch for its partial results");
-        if (H > 65535 || T > 65535) return mllm_fail(1, "attention_bias: %d heads x %d tokens exceed the split kernel's grid", H, T);
+        const int R = H / Hkv;
+        int HG = R >= 4 ? 4 : (R >= 2 ? 2 : 1), KS = 4 / HG;
+        const size_t es = dtype == MLLM_F32 ? 4 : 2, vec = 16 / es;
+        auto bytes = [&](int ks) {
+            const size_t tile = 32 * (size_t)ks;
+            return tile * (dk + vec) * es + ((tile * dv + vec - 1) / vec) * vec * es + sizeof(float) * ((size_t)HG * dk + 4 * (size_t)dv + 8);
+        };
+        while (KS > 1 && bytes(KS) > 96 * 1024) KS /= 2;
+        const size_t smem = bytes(KS);
+        const int chunks = (R + HG - 1) / HG;
+        if ((long long)Hkv * chunks > 65535 || T > 65535) return mllm_fail(1, "attention_bias: %d heads x %d tokens exceed the split kernel's grid", H, T);
+        const dim3 grid(nsplit, Hkv * chunks, T), block(32 * HG * KS);
         if (dtype == MLLM_F32) {
-            MLLM_CUDA(mllm_launch(attention_bias_split_kernel<float>, dim3(nsplit, H, T), dim3(WARPS * 32), 0, stream, true,
+            if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MLLM_CUDA(mllm_launch(attention_bias_split_kernel<float>, grid, block, smem, stream, true,
                                   (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table,
-                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, a));
+                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, HG, KS, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (float*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
         } else {
-            MLLM_CUDA(mllm_launch(attention_bias_split_kernel<bf>, dim3(nsplit, H, T), dim3(WARPS * 32), 0, stream, true,
+            if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MLLM_CUDA(mllm_launch(attention_bias_split_kernel<bf>, grid, block, smem, stream, true,
                                   (const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride,
-                                  token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, a));
+                                  token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, HG, KS, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<bf>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (bf*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
@@ -504,6 +623,52 @@ paged_write_kernel(const T* src, long long row_stride, T* __restrict__ pages, co
     }
 }
 }  // namespace
+
+// keys [T, heads * dk] and values [T, heads * dv] of the step to their page slots in one launch
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+paged_write_kv_kernel(const T* k, long long k_stride, const T* v, long long v_stride, T* __restrict__ k_pages,
+                      T* __restrict__ v_pages, const int* __restrict__ slots, int T_tokens, int heads, int dk, int dv,
+                      int page_size) {
+    pdl_wait();
+    pdl_launch();
+    const int pk = heads * dk, per = heads * (dk + dv);
+    const long long total = (long long)T_tokens * per;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / per), c = (int)(i % per);
+        const int slot = slots[t];
+        if (slot < 0) continue;
+        const size_t row = (size_t)(slot / page_size) * heads;
+        const int off = slot % page_size;
+        if (c < pk) {
+            const int h = c / dk, e = c % dk;
+            k_pages[((row + h) * page_size + off) * dk + e] = k[(size_t)t * k_stride + c];
+        } else {
+            const int cc = c - pk, h = cc / dv, e = cc % dv;
+            v_pages[((row + h) * page_size + off) * dv + e] = v[(size_t)t * v_stride + cc];
+        }
+    }
+}
+}  // namespace
+
+MLLM_EXPORT int mllm_paged_write_kv(const void* k, long long k_stride, const void* v, long long v_stride, void* k_pages,
+                                    void* v_pages, const int* slots, int T, int heads, int dk, int dv, int page_size,
+                                    int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long long total = (long long)T * heads * (dk + dv);
+    const int grid = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(paged_write_kv_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)k, k_stride,
+                              (const float*)v, v_stride, (float*)k_pages, (float*)v_pages, slots, T, heads, dk, dv, page_size));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(paged_write_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
+                              (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, (__nv_bfloat16*)k_pages,
+                              (__nv_bfloat16*)v_pages, slots, T, heads, dk, dv, page_size));
+    else
+        return mllm_fail(1, "paged_write_kv: unknown dtype code %d", dtype);
+    return 0;
+}
 
 MLLM_EXPORT int mllm_paged_write(const void* src, long long row_stride, void* pages, const int* slots, int T, int heads,
                                  int d, int page_size, int dtype, cudaStream_t stream) {

@@ -12,6 +12,15 @@
 // the chunk is staged, then every thread runs CH * RK fused multiply-adds without a barrier; the partial outputs of
 // the row groups meet in shared memory and the warps share the chunk's tokens for the norm.  The order of every sum
 // depends on the sizes only, never on how the tokens were cut into steps.
+//
+// That kernel suits steps of single tokens, where reading and writing the state is all the work.  For prompt portions
+// a second kernel (`wide`) spreads one (request, head) over many more threads, since every element of the state is a
+// recurrence of its own: a CTA takes 32 columns of the state, thread (g, j) keeps rows 4g .. 4g+3 of column j, so a
+// token costs a thread four dependent fused multiply-adds instead of 64; the 32 tokens of a chunk are fetched into
+// registers in one burst before anything is stored (loads and stores in one loop would be serialised, since the
+// compiler cannot tell the global inputs from shared memory), and the raw outputs o_t go to a 32-bit buffer that the
+// RMS norm kernel (csrc/rmsnorm.cu, one row per token and head) finishes.  Both kernels run the same recurrence per
+// state element in the same order, so the state they leave is the same bit for bit.
 #include "common.cuh"
 
 namespace {
@@ -108,7 +117,157 @@ gated_recurrence_kernel(const T* a, const T* z, const T* v, T* __restrict__ y, R
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int WR = 4;               // rows of the state a thread of the wide kernel keeps
+constexpr int WC = 32;              // columns of the state a CTA of the wide kernel takes
+constexpr int WCH = 32;             // tokens per chunk
+constexpr int WLD = 4;              // elements of a and of z that a thread fetches per chunk (32 * 4G / 32G)
+constexpr int WVMAX = 8;            // elements of v a thread fetches ahead at most (32 / G of them: G >= 4)
+
+// grid (requests, heads, ceil(ev / 32)); block (32, G) with G = ceil(ek / 4) row groups.  o [T][Hr*ev] float.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restrict__ o, long long o_stride, RecArgs r) {
+    extern __shared__ __align__(16) float sm[];
+    const int ek = r.ek, ev = r.ev, G = blockDim.y;
+    const int ekp = G * WR;                   // rows padded to a multiple of 4: the padding has f = 1, q = 0
+    float* qs = sm;                           // [WCH][ekp]
+    float* fs = qs + WCH * ekp;               // [WCH][ekp]
+    float* vs = fs + WCH * ekp;               // [WCH][WC]
+    float* os = vs + WCH * WC;                // [G][WCH][WC]
+    pdl_wait();
+    pdl_launch();
+    const int seq = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * WC;
+    const int lane = threadIdx.x, g = threadIdx.y, tid = g * 32 + lane, nthreads = G * 32;
+    const int t0 = r.cu_q[seq], t1 = r.cu_q[seq + 1];
+    const int slot = r.slots[seq];
+    const int j = j0 + lane;
+    const bool col = j < ev;
+    float* sp = r.state + (((size_t)slot * r.Hr + h) * ek) * ev + j;
+    float s[WR];
+#pragma unroll
+    for (int i = 0; i < WR; ++i) s[i] = (col && g * WR + i < ek) ? sp[(size_t)(g * WR + i) * ev] : 0.f;
+
+    // Every thread owns WLD elements of a chunk's a and z (32 * ekp = 4 * threads of them) and VPT = 32 / G of its v:
+    // they are fetched into registers a chunk ahead, while the chunk before is being walked.
+    const int VPT = (WCH * WC + nthreads - 1) / nthreads;       // at most WVMAX when G >= 32 / WVMAX
+    const bool ahead = VPT <= WVMAX;
+    float av[WLD], zv[WLD], vv_next[WVMAX];
+    auto fetch = [&](int c0) {
+        const int n = min(WCH, t1 - c0);
+#pragma unroll
+        for (int u = 0; u < WLD; ++u) {
+            const int idx = tid + u * nthreads, c = idx / ekp, i = idx % ekp;
+            av[u] = zv[u] = 0.f;
+            if (idx < n * ekp && i < ek) {
+                av[u] = to_f32(a[(size_t)(c0 + c) * r.a_stride + (size_t)h * ek + i]);
+                zv[u] = to_f32(z[(size_t)(c0 + c) * r.z_stride + (size_t)h * ek + i]);
+            }
+        }
+        if (ahead) {
+#pragma unroll
+            for (int u = 0; u < WVMAX; ++u) {
+                const int idx = tid + u * nthreads, c = idx / WC, d = idx % WC;
+                vv_next[u] = (u < VPT && idx < n * WC && j0 + d < ev)
+                                 ? to_f32(v[(size_t)(c0 + c) * r.v_stride + (size_t)h * ev + j0 + d]) : 0.f;
+            }
+        }
+    };
+    if (t0 < t1) fetch(t0);
+    for (int c0 = t0; c0 < t1; c0 += WCH) {
+        const int n = min(WCH, t1 - c0);
+        __syncthreads();                      // the chunk before is no longer read
+#pragma unroll
+        for (int u = 0; u < WLD; ++u) {
+            const int idx = tid + u * nthreads, i = idx % ekp;
+            if (idx >= n * ekp) continue;
+            float qv = 0.f, fv = 1.f;
+            if (i < ek) {
+                const float lo = r.lower[h * ek + i];
+                qv = av[u] / (1.0f + expf(-av[u]));
+                fv = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-(zv[u] + r.f_bias[h * ek + i]))));
+            }
+            qs[idx] = qv;
+            fs[idx] = fv;
+        }
+        if (ahead) {
+#pragma unroll
+            for (int u = 0; u < WVMAX; ++u) {
+                const int idx = tid + u * nthreads;
+                if (u < VPT && idx < n * WC) vs[idx] = vv_next[u];
+            }
+        } else {
+            for (int base = tid; base < n * WC; base += nthreads * WLD) {
+                float vv[WLD];
+#pragma unroll
+                for (int u = 0; u < WLD; ++u) {
+                    const int idx = base + u * nthreads, c = idx / WC, d = idx % WC;
+                    vv[u] = (idx < n * WC && j0 + d < ev) ? to_f32(v[(size_t)(c0 + c) * r.v_stride + (size_t)h * ev + j0 + d]) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < WLD; ++u) {
+                    const int idx = base + u * nthreads;
+                    if (idx < n * WC) vs[idx] = vv[u];
+                }
+            }
+        }
+        if (c0 + WCH < t1) fetch(c0 + WCH);   // the next chunk's loads are in flight during this chunk's walk
+        __syncthreads();
+        for (int c = 0; c < n; ++c) {
+            const float vv = vs[c * WC + lane];
+            const float4 f4 = *reinterpret_cast<const float4*>(fs + c * ekp + g * WR);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + c * ekp + g * WR);
+            s[0] = fmaf(f4.x, s[0], (1.0f - f4.x) * vv);
+            s[1] = fmaf(f4.y, s[1], (1.0f - f4.y) * vv);
+            s[2] = fmaf(f4.z, s[2], (1.0f - f4.z) * vv);
+            s[3] = fmaf(f4.w, s[3], (1.0f - f4.w) * vv);
+            os[(g * WCH + c) * WC + lane] = fmaf(s[3], q4.w, fmaf(s[2], q4.z, fmaf(s[1], q4.y, s[0] * q4.x)));
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n * WC; idx += nthreads) {          // row groups meet in group order
+            const int c = idx / WC, d = idx % WC;
+            float acc = os[c * WC + d];
+            for (int gg = 1; gg < G; ++gg) acc += os[(gg * WCH + c) * WC + d];
+            if (j0 + d < ev) o[(size_t)(c0 + c) * o_stride + (size_t)h * ev + j0 + d] = acc;
+        }
+    }
+    if (r.write_state && col) {
+#pragma unroll
+        for (int i = 0; i < WR; ++i)
+            if (g * WR + i < ek) sp[(size_t)(g * WR + i) * ev] = s[i];
+    }
+}
+
 }  // namespace
+
+// The recurrence alone for prompt portions: o [T][Hr*ev] (32-bit, un-normed).  ek up to 128.
+MLLM_EXPORT int mllm_gated_recurrence_wide(const void* a, long long a_stride, const void* z, long long z_stride,
+                                           const void* v, long long v_stride, const float* f_bias, const float* lower,
+                                           float* state, const int* cu_q, const int* slots, float* o, long long o_stride,
+                                           int S, int Hr, int ek, int ev, int write_state, int dtype, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (ek <= 0 || ev <= 0 || Hr <= 0) return mllm_fail(1, "gated_recurrence: sizes %d x %d x %d", Hr, ek, ev);
+    const int G = (ek + WR - 1) / WR;
+    if (G > 32) return mllm_fail(1, "gated_recurrence: the wide kernel takes states of up to %d rows, not %d", 32 * WR, ek);
+    if (Hr > 65535 || (ev + WC - 1) / WC > 65535) return mllm_fail(1, "gated_recurrence: sizes exceed the grid");
+    const size_t smem = sizeof(float) * ((size_t)2 * WCH * G * WR + WCH * WC + (size_t)G * WCH * WC);
+    RecArgs r{cu_q, slots, f_bias, lower, nullptr, state, a_stride, z_stride, v_stride, 0,
+              Hr, ek, ev, 0, G, WCH, write_state, 0.f, 1.f};
+    const dim3 grid(S, Hr, (ev + WC - 1) / WC), block(32, G);
+    using bf = __nv_bfloat16;
+    if (dtype == MLLM_F32) {
+        MLLM_CUDA(cudaFuncSetAttribute(gated_recurrence_wide_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MLLM_CUDA(mllm_launch(gated_recurrence_wide_kernel<float>, grid, block, smem, stream, true, (const float*)a,
+                              (const float*)z, (const float*)v, o, o_stride, r));
+    } else if (dtype == MLLM_BF16) {
+        MLLM_CUDA(cudaFuncSetAttribute(gated_recurrence_wide_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MLLM_CUDA(mllm_launch(gated_recurrence_wide_kernel<bf>, grid, block, smem, stream, true, (const bf*)a, (const bf*)z,
+                              (const bf*)v, o, o_stride, r));
+    } else {
+        return mllm_fail(1, "gated_recurrence: unknown dtype code %d", dtype);
+    }
+    return 0;
+}
 
 MLLM_EXPORT int mllm_gated_recurrence(const void* a, long long a_stride, const void* z, long long z_stride, const void* v,
                                       long long v_stride, const float* f_bias, const float* lower, const float* norm_w,

@@ -2,6 +2,8 @@
 // written as 32-bit or bfloat16.  `offset` is 1 for weights that are stored around zero and 0 for plain
 // weights.  A second weight vector and output may be given: two norms of the same rows that differ only
 // in their weights (the two branches of a parallel block) then cost one read of x and one sum of squares.
+// With `heads` > 1 a row of x and of the output holds that many vectors of width D side by side, each normed on its
+// own with the same weights (the per-head norm of a mixer's outputs); `scale` multiplies the result.
 // All arithmetic is 32-bit; the sum of squares runs in an order that depends on the width only.
 #include "common.cuh"
 
@@ -10,19 +12,22 @@ namespace {
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* x, long long x_stride, const int* __restrict__ rows,
                                const float* __restrict__ w1, const float* __restrict__ w2, TOut* __restrict__ out1,
-                               TOut* __restrict__ out2, int D, float eps, float offset) {
+                               TOut* __restrict__ out2, long long out_stride, int heads, int D, float eps, float offset,
+                               float scale) {
     __shared__ float scratch[33];
     pdl_wait();
     pdl_launch();
-    const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+    const int r = blockIdx.x / heads, hd = blockIdx.x % heads;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride + (size_t)hd * D;
+    out1 += (size_t)r * out_stride + (size_t)hd * D;
+    if (out2) out2 += (size_t)r * out_stride + (size_t)hd * D;
     float q = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) q = fmaf(xr[d], xr[d], q);
-    const float inv = 1.0f / sqrtf(block_sum(q, scratch) / (float)D + eps);
+    const float inv = scale / sqrtf(block_sum(q, scratch) / (float)D + eps);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         const float y = xr[d] * inv;
-        out1[(size_t)r * D + d] = from_f32<TOut>(y * (w1[d] + offset));
-        if (out2) out2[(size_t)r * D + d] = from_f32<TOut>(y * (w2[d] + offset));
+        out1[d] = from_f32<TOut>(y * (w1[d] + offset));
+        if (out2) out2[d] = from_f32<TOut>(y * (w2[d] + offset));
     }
 }
 
@@ -43,14 +48,17 @@ __device__ __forceinline__ void store4(TOut* o, float y0, float y1, float y2, fl
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 rmsnorm_warp_kernel(const float* x, long long x_stride, const int* __restrict__ rows, const float* __restrict__ w1,
-                    const float* __restrict__ w2, TOut* __restrict__ out1, TOut* __restrict__ out2, int R, int D,
-                    float eps, float offset) {
+                    const float* __restrict__ w2, TOut* __restrict__ out1, TOut* __restrict__ out2, long long out_stride,
+                    int heads, int R, int D, float eps, float offset, float scale) {
     constexpr int KEEP = 16;
     pdl_wait();
     pdl_launch();
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= R) return;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+    const int rh = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (rh >= R * heads) return;
+    const int r = rh / heads, hd = rh % heads;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride + (size_t)hd * D;
+    out1 += (size_t)r * out_stride + (size_t)hd * D;
+    if (out2) out2 += (size_t)r * out_stride + (size_t)hd * D;
     float4 v[KEEP];
     float q = 0.f;
 #pragma unroll
@@ -59,18 +67,18 @@ rmsnorm_warp_kernel(const float* x, long long x_stride, const int* __restrict__ 
         v[i] = k < D ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
     }
-    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)D + eps);
+    const float inv = scale / sqrtf(warp_sum(q) / (float)D + eps);
 #pragma unroll
     for (int i = 0; i < KEEP; ++i) {
         const int k = lane * 4 + i * 128;
         if (k >= D) break;
         const float y0 = v[i].x * inv, y1 = v[i].y * inv, y2 = v[i].z * inv, y3 = v[i].w * inv;
         const float4 g = __ldg(reinterpret_cast<const float4*>(w1 + k));
-        store4<TOut>(out1 + (size_t)r * D + k, y0 * (g.x + offset), y1 * (g.y + offset), y2 * (g.z + offset),
+        store4<TOut>(out1 + k, y0 * (g.x + offset), y1 * (g.y + offset), y2 * (g.z + offset),
                      y3 * (g.w + offset));
         if (out2) {
             const float4 g2 = __ldg(reinterpret_cast<const float4*>(w2 + k));
-            store4<TOut>(out2 + (size_t)r * D + k, y0 * (g2.x + offset), y1 * (g2.y + offset), y2 * (g2.z + offset),
+            store4<TOut>(out2 + k, y0 * (g2.x + offset), y1 * (g2.y + offset), y2 * (g2.z + offset),
                          y3 * (g2.w + offset));
         }
     }
@@ -78,17 +86,20 @@ rmsnorm_warp_kernel(const float* x, long long x_stride, const int* __restrict__ 
 
 template <typename TOut>
 int launch(const float* x, long long x_stride, const int* rows, const float* w1, const float* w2, void* out1, void* out2,
-           int R, int D, float eps, float offset, cudaStream_t stream) {
+           long long out_stride, int heads, int R, int D, float eps, float offset, float scale, cudaStream_t stream) {
+    constexpr int OV = 16 / sizeof(TOut);       // output elements per 16 bytes (stores are 16 or 8 bytes of 4 values)
     const bool fast = D % 4 == 0 && D <= 2048 && x_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w1 % 16 == 0 &&
-                      (uintptr_t)out1 % 16 == 0 && (!out2 || ((uintptr_t)w2 % 16 == 0 && (uintptr_t)out2 % 16 == 0));
+                      (uintptr_t)out1 % 16 == 0 && out_stride % OV == 0 && (heads == 1 || D % OV == 0) &&
+                      (!out2 || ((uintptr_t)w2 % 16 == 0 && (uintptr_t)out2 % 16 == 0));
+    if ((long long)R * heads > 2147483647LL) return mllm_fail(1, "rmsnorm: too many rows");
     if (fast) {
-        MLLM_CUDA(mllm_launch(rmsnorm_warp_kernel<TOut>, dim3((R + 7) / 8), dim3(256), 0, stream, true, x, x_stride, rows,
-                              w1, w2, (TOut*)out1, (TOut*)out2, R, D, eps, offset));
+        MLLM_CUDA(mllm_launch(rmsnorm_warp_kernel<TOut>, dim3((R * heads + 7) / 8), dim3(256), 0, stream, true, x, x_stride,
+                              rows, w1, w2, (TOut*)out1, (TOut*)out2, out_stride, heads, R, D, eps, offset, scale));
         return 0;
     }
     const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
-    MLLM_CUDA(mllm_launch(rmsnorm_kernel<TOut>, dim3(R), dim3(threads), 0, stream, true, x, x_stride, rows, w1, w2,
-                          (TOut*)out1, (TOut*)out2, D, eps, offset));
+    MLLM_CUDA(mllm_launch(rmsnorm_kernel<TOut>, dim3(R * heads), dim3(threads), 0, stream, true, x, x_stride, rows, w1, w2,
+                          (TOut*)out1, (TOut*)out2, out_stride, heads, D, eps, offset, scale));
     return 0;
 }
 
@@ -113,14 +124,16 @@ gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long lon
 }  // namespace
 
 MLLM_EXPORT int mllm_rmsnorm(const float* x, long long x_stride, const int* rows, const float* w1, const float* w2,
-                             void* out1, void* out2, int R, int D, float eps, float offset, int out_dtype,
-                             cudaStream_t stream) {
+                             void* out1, void* out2, long long out_stride, int heads, int R, int D, float eps,
+                             float offset, float scale, int out_dtype, cudaStream_t stream) {
     if (R <= 0) return 0;
-    if (D <= 0) return mllm_fail(1, "rmsnorm: width %d", D);
+    if (D <= 0 || heads <= 0) return mllm_fail(1, "rmsnorm: width %d, heads %d", D, heads);
     if ((w2 == nullptr) != (out2 == nullptr)) return mllm_fail(1, "rmsnorm: the second weight and output come together");
-    if (out_dtype == MLLM_F32) return launch<float>(x, x_stride, rows, w1, w2, out1, out2, R, D, eps, offset, stream);
+    if (out_dtype == MLLM_F32)
+        return launch<float>(x, x_stride, rows, w1, w2, out1, out2, out_stride, heads, R, D, eps, offset, scale, stream);
     if (out_dtype == MLLM_BF16)
-        return launch<__nv_bfloat16>(x, x_stride, rows, w1, w2, out1, out2, R, D, eps, offset, stream);
+        return launch<__nv_bfloat16>(x, x_stride, rows, w1, w2, out1, out2, out_stride, heads, R, D, eps, offset, scale,
+                                     stream);
     return mllm_fail(1, "rmsnorm: unknown dtype code %d", out_dtype);
 }
 

@@ -85,10 +85,15 @@ def _signatures(lib):
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_attention_tiled_wide": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                       c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
-        "mllm_rmsnorm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
-                         c_int, c_void_p],
+        "mllm_rmsnorm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float,
+                         c_float, c_float, c_int, c_void_p],
+        "mllm_gated_recurrence_wide": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p],
         "mllm_gated_act": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_paged_write": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_paged_write_kv": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p],
         "mllm_attention_bias_split_keys": [],
         "mllm_attention_bias": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -336,24 +341,27 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
           beta.data_ptr(), out.data_ptr(), R, D, float(eps), _dt(out), _stream())
 
 
-def rmsnorm(x, weight, eps: float, out, rows=None, unit_offset: bool = True, weight2=None, out2=None) -> None:
-    """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * (weight + 1) (or * weight when ``unit_offset`` is False);
-    x 32-bit, out 32-bit or bfloat16.  ``weight2`` / ``out2``: a second norm of the same rows with other weights,
-    from the same sum of squares."""
+def rmsnorm(x, weight, eps: float, out, rows=None, unit_offset: bool = True, weight2=None, out2=None, heads: int = 1,
+            scale: float = 1.0) -> None:
+    """out[r] = scale * x[r] / sqrt(mean(x[r]^2) + eps) * (weight + 1) (or * weight when ``unit_offset`` is False);
+    x 32-bit, out 32-bit or bfloat16 (rows contiguous: a column slice of a wider buffer is fine).  ``weight2`` /
+    ``out2``: a second norm of the same rows with other weights, from the same sum of squares.  ``heads`` > 1: a row
+    is that many vectors side by side, each normed on its own with the same weights."""
     _cuda("x", x, torch.float32, contiguous=False)
     _cuda("weight", weight, torch.float32)
-    _cuda("out", out)
+    _cuda("out", out, contiguous=False)
     ldx = _rows("x", x)
-    D = x.shape[1]
+    ldo = _rows("out", out)
+    D = x.shape[1] // heads
     R = out.shape[0]
-    if weight.numel() != D or out.shape[1] != D:
-        raise KernelError(f"rmsnorm: width {D} against weight {weight.numel()}, out {tuple(out.shape)}")
+    if weight.numel() != D or out.shape[1] != D * heads or x.shape[1] != D * heads:
+        raise KernelError(f"rmsnorm: width {D} x {heads} against weight {weight.numel()}, out {tuple(out.shape)}")
     if (weight2 is None) != (out2 is None):
         raise KernelError("rmsnorm: the second weight and the second output come together")
     if weight2 is not None:
         _cuda("weight2", weight2, torch.float32)
-        _cuda("out2", out2, out.dtype)
-        if weight2.numel() != D or tuple(out2.shape) != tuple(out.shape):
+        _cuda("out2", out2, out.dtype, contiguous=False)
+        if weight2.numel() != D or tuple(out2.shape) != tuple(out.shape) or _rows("out2", out2) != ldo:
             raise KernelError("rmsnorm: the second weight or output does not fit the first")
     if rows is not None:
         _cuda("rows", rows, torch.int32)
@@ -363,7 +371,8 @@ def rmsnorm(x, weight, eps: float, out, rows=None, unit_offset: bool = True, wei
         raise KernelError("rmsnorm: x and out differ in rows")
     _call("mllm_rmsnorm", x.data_ptr(), ldx, rows.data_ptr() if rows is not None else None, weight.data_ptr(),
           weight2.data_ptr() if weight2 is not None else None, out.data_ptr(),
-          out2.data_ptr() if out2 is not None else None, R, D, float(eps), 1.0 if unit_offset else 0.0, _dt(out), _stream())
+          out2.data_ptr() if out2 is not None else None, ldo, int(heads), R, D, float(eps), 1.0 if unit_offset else 0.0,
+          float(scale), _dt(out), _stream())
 
 
 def gated_act(gu, out, act: str) -> None:
@@ -702,6 +711,25 @@ def paged_write(src, pages, slot_mapping) -> None:
           ps, _dt(src), _stream())
 
 
+def paged_write_kv(k, v, k_pages, v_pages, slot_mapping) -> None:
+    """Keys k [T, heads * dk] and values v [T, heads * dv] (rows contiguous) to their slots in k_pages
+    [num_pages, heads, page_size, dk] and v_pages [num_pages, heads, page_size, dv], in one launch."""
+    _cuda("k", k, contiguous=False)
+    _cuda("v", v, k.dtype, contiguous=False)
+    _cuda("k_pages", k_pages, k.dtype)
+    _cuda("v_pages", v_pages, k.dtype)
+    _cuda("slot_mapping", slot_mapping, torch.int32)
+    _, heads, ps, dk = k_pages.shape
+    dv = v_pages.shape[3]
+    T = k.shape[0]
+    if tuple(k.shape) != (T, heads * dk) or tuple(v.shape) != (T, heads * dv) or slot_mapping.numel() != T \
+            or v_pages.shape[:3] != k_pages.shape[:3]:
+        raise KernelError(f"paged_write_kv: k {tuple(k.shape)}, v {tuple(v.shape)} against pages {tuple(k_pages.shape)}, "
+                          f"{tuple(v_pages.shape)}")
+    _call("mllm_paged_write_kv", k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v), k_pages.data_ptr(),
+          v_pages.data_ptr(), slot_mapping.data_ptr(), T, heads, dk, dv, ps, _dt(k), _stream())
+
+
 BIAS_ATTN_MAX_DIM = 256        # largest key and value size of csrc/attention_bias.cu
 _bias_split_keys = None
 
@@ -776,12 +804,18 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
         launches += 1           # the kernel that merges the splits
 
 
+REC_WIDE_MAX_ROWS = 128        # rows of a head's state that the kernel for prompt portions takes
+recurrence_launches = {}       # "step" / "wide" -> launches so far
+
+
 def gated_recurrence(a, z, v, f_bias, lower, norm_weight, eps: float, state, ctx, out, *, heads: int, out_scale: float = 1.0,
-                     write_state: bool = True) -> None:
+                     write_state: bool = True, impl: Optional[str] = None) -> None:
     """The gated linear recurrence of csrc/gated_recurrence.cu over the step's tokens, request by request:
     f = lower + (1 - lower) * sigmoid(z + f_bias); S <- diag(f) S + (1 - f) v^T; o = S^T silu(a);
     out = out_scale * rms_norm(o) * norm_weight per head.  a, z [T, heads * ek], v, out [T, heads * ev] (rows
-    contiguous; column slices are fine), state [slots, heads, ek, ev] float32, indexed by ctx.state_slots."""
+    contiguous; column slices are fine), state [slots, heads, ek, ev] float32, indexed by ctx.state_slots.
+    ``impl``: "step" (one CTA per request and head with the norm fused: single tokens) or "wide" (the recurrence
+    spread over 32-column CTAs, then the norm kernel: prompt portions); None picks by the step's shape."""
     _cuda("a", a, contiguous=False)
     _cuda("z", z, a.dtype, contiguous=False)
     _cuda("v", v, a.dtype, contiguous=False)
@@ -797,6 +831,22 @@ def gated_recurrence(a, z, v, f_bias, lower, norm_weight, eps: float, state, ctx
             or tuple(out.shape) != (T, heads * ev) or f_bias.numel() != heads * ek or lower.numel() != heads * ek \
             or norm_weight.numel() != ev:
         raise KernelError("gated_recurrence: shapes do not fit the state")
+    if impl is None:
+        impl = "wide" if (T > ctx.S and ek <= REC_WIDE_MAX_ROWS) else "step"
+    recurrence_launches[impl] = recurrence_launches.get(impl, 0) + 1
+    if impl == "wide":
+        # prompt portions: the recurrence spread over many threads, raw outputs in 32-bit, then the per-head norm
+        if ek > REC_WIDE_MAX_ROWS:
+            raise KernelError(f"gated_recurrence: the wide kernel takes states of up to {REC_WIDE_MAX_ROWS} rows, not {ek}")
+        raw = ctx.ws.buf("rec_raw", T, heads * ev, torch.float32)
+        _call("mllm_gated_recurrence_wide", a.data_ptr(), _rows("a", a), z.data_ptr(), _rows("z", z), v.data_ptr(),
+              _rows("v", v), f_bias.data_ptr(), lower.data_ptr(), state.data_ptr(), ctx.cu_q.data_ptr(),
+              ctx.state_slots.data_ptr(), raw.data_ptr(), _rows("raw", raw), ctx.S, heads, ek, ev, int(write_state),
+              _dt(a), _stream())
+        rmsnorm(raw, norm_weight, eps, out, unit_offset=False, heads=heads, scale=out_scale)
+        return
+    if impl != "step":
+        raise KernelError(f"gated_recurrence: unknown implementation {impl!r}")
     _call("mllm_gated_recurrence", a.data_ptr(), _rows("a", a), z.data_ptr(), _rows("z", z), v.data_ptr(), _rows("v", v),
           f_bias.data_ptr(), lower.data_ptr(), norm_weight.data_ptr(), state.data_ptr(), ctx.cu_q.data_ptr(),
           ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S, heads, ek, ev, float(eps), float(out_scale),

@@ -170,8 +170,8 @@ class DistanceBiasAttention(ProjectedMixer):
         gv = ctx.groups[cache.group]
         q = proj[:, :self.q_size]
         if cache.write:
-            ops.paged_write(proj[:, self.q_size:self.q_size + self.k_size], cache.k_pages, gv.slot_mapping)
-            ops.paged_write(proj[:, self.q_size + self.k_size:], cache.v_pages, gv.slot_mapping)
+            ops.paged_write_kv(proj[:, self.q_size:self.q_size + self.k_size], proj[:, self.q_size + self.k_size:],
+                               cache.k_pages, cache.v_pages, gv.slot_mapping)
         ops.biased_attention(q, cache.k_pages, cache.v_pages, gv.block_table, ctx, out, num_heads=self.num_heads,
                              num_kv_heads=self.num_kv_heads, scale=self.scale, dist_bias=self.dist_bias,
                              q_scale=self.q_scale, out_scale=out_scale, window=self.window)

@@ -32,6 +32,20 @@ def _tol(dtype):
 
 # ------------------------------------------------------------------------------------------------ norm, activation
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,D", [(3, 40), (2, 33), (5, 256)])
+def test_rmsnorm_per_head_into_a_column_slice(ops, out_dtype, heads, D):
+    R, eps = 9, 1e-5
+    x = rnd(R, heads * D, seed=1, scale=2.0)
+    w = rnd(D, seed=2) + 1.0
+    wide = torch.zeros(R, heads * D + 16, device=DEV, dtype=out_dtype)
+    out = wide[:, 16:]
+    ops.rmsnorm(x, w, eps, out, unit_offset=False, heads=heads, scale=0.6)
+    want = 0.6 * P.rms_norm(x.double().cpu().view(R, heads, D), w.double().cpu(), eps, False).reshape(R, heads * D)
+    assert (out.double().cpu() - want).abs().max() < _tol(out_dtype) * max(1.0, want.abs().max().item())
+    assert torch.all(wide[:, :16] == 0)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("R,D,eps", [(5, 48, 1e-5), (33, 1600, 1e-6), (3, 1001, 1e-3), (2, 4096, 1e-5), (1, 8, 0.5)])
 def test_rmsnorm(ops, out_dtype, R, D, eps):
     x = rnd(R, D, seed=4, scale=3.0) + 0.5
@@ -92,6 +106,22 @@ def test_paged_write(ops, dtype):
         s = int(slots[t])
         assert torch.equal(pool[s // page, :, s % page].reshape(-1), src[t])
     assert int((pool != 0).sum()) <= T * heads * d
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_paged_write_kv(ops, dtype):
+    T, heads, dk, dv, page, pages = 23, 2, 16, 5, 8, 7
+    wide = rnd(T, heads * (dk + dv) + 3, seed=8, dtype=dtype)
+    k, v = wide[:, 3:3 + heads * dk], wide[:, 3 + heads * dk:]
+    kp = torch.zeros(pages, heads, page, dk, device=DEV, dtype=dtype)
+    vp = torch.zeros(pages, heads, page, dv, device=DEV, dtype=dtype)
+    g = torch.Generator().manual_seed(10)
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32).to(DEV)
+    ops.paged_write_kv(k, v, kp, vp, slots)
+    for t in range(T):
+        s = int(slots[t])
+        assert torch.equal(kp[s // page, :, s % page].reshape(-1), k[t])
+        assert torch.equal(vp[s // page, :, s % page].reshape(-1), v[t])
 
 
 # ------------------------------------------------------------------------------------------------ attention
@@ -272,6 +302,9 @@ def test_distance_bias_attention_refuses_sizes_it_cannot_take(ops):
 
 
 # ------------------------------------------------------------------------------------------------ recurrence
+_WS = {}
+
+
 def _rec_ctx(q_lens, slots):
     ctx = _Ctx()
     cu = [0]
@@ -280,12 +313,18 @@ def _rec_ctx(q_lens, slots):
     ctx.cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
     ctx.state_slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
     ctx.S = len(q_lens)
+    from mini_llm_b200.engine.context import Workspace
+    ctx.ws = _WS.setdefault("ws", Workspace(torch.device(DEV), 64))
     return ctx
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hr,ek,ev", [(2, 16, 40), (3, 8, 16), (1, 64, 64), (2, 96, 33), (1, 130, 96), (4, 32, 1), (1, 1, 32)])
-def test_gated_recurrence_in_portions_and_batches(ops, dtype, Hr, ek, ev):
+@pytest.mark.parametrize("Hr,ek,ev", [(2, 16, 40), (3, 8, 16), (1, 64, 64), (2, 96, 33), (1, 130, 96), (4, 32, 1), (1, 1, 32),
+                                      (2, 128, 130), (1, 6, 200)])
+@pytest.mark.parametrize("impl", [None, "step", "wide"])
+def test_gated_recurrence_in_portions_and_batches(ops, dtype, impl, Hr, ek, ev):
+    if impl == "wide" and ek > ops.REC_WIDE_MAX_ROWS:
+        pytest.skip("the kernel for prompt portions takes up to 128 rows")
     eps, out_scale = 1e-5, 0.9
     lens = [45, 3, 20]
     g = torch.Generator().manual_seed(Hr * 7 + ek)
@@ -318,7 +357,7 @@ def test_gated_recurrence_in_portions_and_batches(ops, dtype, Hr, ek, ev):
         a, z, v = wide[:, :Hr * ek], wide[:, Hr * ek:2 * Hr * ek], wide[:, 2 * Hr * ek:]
         out = torch.empty(T, Hr * ev, device=DEV, dtype=dtype)
         ops.gated_recurrence(a, z, v, f_bias, lower, norm_w, eps, state, _rec_ctx(ns, [slots[s] for s in live]), out,
-                             heads=Hr, out_scale=out_scale)
+                             heads=Hr, out_scale=out_scale, impl=impl)
         k = 0
         for s, n in zip(live, ns):
             got[s].append(out[k:k + n].double().cpu())
@@ -329,6 +368,21 @@ def test_gated_recurrence_in_portions_and_batches(ops, dtype, Hr, ek, ev):
     for s in cuts:
         assert (torch.cat(got[s]) - want[s]).abs().max() < tol * max(1.0, want[s].abs().max().item()), s
     assert torch.all(state[3] == 7.0) and torch.all(state[1] == 0.0)
+
+
+def test_gated_recurrence_kernels_leave_the_same_state(ops):
+    Hr, ek, ev, n = 2, 24, 72, 70
+    a, z, v = rnd(n, Hr * ek, seed=1), rnd(n, Hr * ek, seed=2, scale=2.0), rnd(n, Hr * ev, seed=3)
+    fb, lo, nw = rnd(Hr * ek, seed=4), torch.rand(Hr * ek, device=DEV), torch.rand(ev, device=DEV) + 0.5
+    states, outs = [], []
+    for impl in ("step", "wide"):
+        state = torch.zeros(1, Hr, ek, ev, device=DEV)
+        out = torch.empty(n, Hr * ev, device=DEV)
+        ops.gated_recurrence(a, z, v, fb, lo, nw, 1e-5, state, _rec_ctx([n], [0]), out, heads=Hr, impl=impl)
+        states.append(state)
+        outs.append(out)
+    assert torch.equal(states[0], states[1])
+    assert (outs[0] - outs[1]).abs().max() < 1e-5
 
 
 def test_gated_recurrence_reads_without_writing(ops):
