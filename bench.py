@@ -302,7 +302,7 @@ def run_prefill(model_dir, dtype, iters=5, warmup=3):
     return dict(ms=ms, tok_s=PREFILL_TOKENS / (ms / 1e3), flops=fl)
 
 
-def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: bool = False) -> int:
+def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: bool = False, design: str = "gpt2") -> int:
     """One eager prefill step (2 x 1024 tokens) or a few eager decode steps at GPT-2 small's
     layer sizes with ``layers`` layers: a small, bounded workload to put under ncu, e.g.
     ncu --set full --clock-control none -k regex:attention_flash -c 1 python bench.py --profile-step prefill --layers 2
@@ -316,9 +316,14 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: b
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = dict(SMALL, n_layer=layers)
+    if design == "finuvik":                      # the same step of Finuvik at the "small" comparison size
+        cfg = design_configs("small")["finuvik"]
+        cfg["layers"] = cfg["layers"][:layers]
+        cfg["n_positions"], cfg["vocab_size"] = cfg["max_positions"], cfg["vocab"]      # the names used below
     times = None
     with tempfile.TemporaryDirectory(prefix="mini_llm_prof_") as d:
-        m.write_random_model(cfg, 0, d, dtype=dtype)
+        m.write_random_model({k: v for k, v in cfg.items() if design != "finuvik" or k not in ("n_positions", "vocab_size")},
+                             0, d, dtype=dtype)
         n = cfg["n_positions"]
         B = 2 if kind == "prefill" else batch
         runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=B * n, max_num_seqs=B,
@@ -355,7 +360,7 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: b
                      for name, k, ms in rows}
         torch.cuda.synchronize()
         ops.check_device_errors()
-    line = {"profile_step": kind, "layers": layers, "batch": B, "dtype": dtype, "launches": ops.launches}
+    line = {"profile_step": kind, "design": design, "layers": layers, "batch": B, "dtype": dtype, "launches": ops.launches}
     if times is not None:
         line["kernel_times"] = times
         line["kernel_us_total"] = round(sum(v["us"] for v in times.values()), 1)
@@ -702,6 +707,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64, prefill and other-precision measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
+    ap.add_argument("--design", choices=["gpt2", "finuvik"], default="gpt2",
+                    help="with --profile-step: the model whose step is run (finuvik: the 'small' size of --compare-designs)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --profile-step: time every launch of one eager step with CUDA events and print the shares")
     ap.add_argument("--attention", choices=["auto", "mma_sync"], default="auto",
@@ -724,7 +731,7 @@ def main() -> int:
         from mini_llm_b200 import ops
         ops.use_tcgen05_attention = False
     if args.profile_step:
-        return profile_step(args.profile_step, args.dtype, args.layers, args.batch, args.kernel_times)
+        return profile_step(args.profile_step, args.dtype, args.layers, args.batch, args.kernel_times, args.design)
     if args.workload:
         return run_workload(args.workload, args.dtype, args.layers if args.layers != SMALL["n_layer"] else 0)
     if args.impl == "reference":

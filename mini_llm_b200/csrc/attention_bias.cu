@@ -8,7 +8,7 @@
 // window is set); softmax over the visible keys; out_i = out_scale * sum_j p_ij v_j.  Either table may be absent.
 // Scores, biases, softmax and the weighted sum are 32-bit (expf, not the fast intrinsic) for both cache dtypes.
 //
-// Three kernels.  `simt`: one warp per (token, head), 32 keys at a time: any step, and the plain twin of the
+// Four kernels (the fourth, `mma`, is described where it stands).  `simt`: one warp per (token, head), 32 keys at a time: any step, and the plain twin of the
 // others.  `tiled`: 64 queries x 32 keys per CTA and head for prompt portions: queries in shared memory, a key
 // tile staged transposed and a value tile as it is, 2 x 4 scores and 2 x dv/8 outputs per thread.  `split`: single
 // tokens (decode): the keys of a token are cut into splits of 256 starting at multiples of 256 from position 0, a
@@ -509,6 +509,228 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
     }
 }
 
+// ------------------------------------------------------------------------------------------------ prompt portions, bfloat16
+// The same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit accumulators) for key and value
+// sizes that are multiples of 16 up to 128.  A CTA of four warps takes one tile of up to 64 new tokens and one head;
+// a warp owns 16 query rows.  Key tile j covers the absolute positions [64j, 64j + 64).  Keys and values come into
+// shared memory by cp.async (rows nobody sees are zero-filled), the next tile's while the current one is used.
+// S = Q K^T is accumulated in 32-bit; the query's factor, the scale and the distance bias are applied to the 32-bit
+// sums; the online softmax is 32-bit (scores in units of ln 2 and exp2f); the weights go into the second product as p = hi + lo, two bfloat16
+// terms, so that they keep about 16 bits; the output sums are 32-bit.
+constexpr int MQ = 64, MK = 64, MMAX = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;                                // 0 bytes read: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(128)
+attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages,
+                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tiles,
+                          const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, long long out_stride, int H,
+                          int Hkv, int dk, int dv, int page_size, BiasArgs a) {
+    using bf = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int qrow = dk + 8, krow = dk + 8, vrow = dv + 8;       // 16 bytes of padding: ldmatrix rows fall on different banks
+    bf* Qs = reinterpret_cast<bf*>(smraw);                       // [MQ][dk+8]
+    bf* Ks = Qs + MQ * qrow;                                     // [2][MK][dk+8]
+    bf* Vs = Ks + 2 * MK * krow;                                 // [2][MK][dv+8]
+    float* Bs = reinterpret_cast<float*>(Vs + 2 * MK * vrow);    // [2][MQ+MK] the head's bias at the distances of a tile pair
+    pdl_wait();
+    pdl_launch();
+    const int tile = blockIdx.y, h = blockIdx.x;
+    const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
+    const int pos0 = positions[tok0], pos_max = pos0 + rows - 1;
+    const int hk = h / (H / Hkv);
+    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int first_key = 0;
+    if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
+    const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
+    const int kp8 = dk / 8, vp8 = dv / 8;
+
+    auto stage = [&](int j, int buf) {                           // key tile j into buffer buf
+        bf* kd = Ks + buf * MK * krow;
+        bf* vd = Vs + buf * MK * vrow;
+        for (int i = tid; i < MK * kp8; i += 128) {
+            const int key = i / kp8, piece = i % kp8, kp = j * MK + key;
+            const bool ok = kp <= pos_max && kp >= first_key;
+            const bf* src = ok ? k_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dk + piece * 8 : k_pages;
+            cp_async16(kd + key * krow + piece * 8, src, ok);
+        }
+        for (int i = tid; i < MK * vp8; i += 128) {
+            const int key = i / vp8, piece = i % vp8, kp = j * MK + key;
+            const bool ok = kp <= pos_max && kp >= first_key;
+            const bf* src = ok ? v_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dv + piece * 8 : v_pages;
+            cp_async16(vd + key * vrow + piece * 8, src, ok);
+        }
+        if (brow) {
+            const int dist0 = pos0 - (j * MK + MK - 1);
+            for (int i = tid; i < MQ + MK; i += 128) {
+                const int dist = dist0 + i;
+                Bs[buf * (MQ + MK) + i] = (dist >= 0 && dist < a.n_dist) ? brow[dist] * LOG2E : 0.f;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int j_first = first_key / MK, j_last = pos_max / MK;
+    for (int i = tid; i < MQ * kp8; i += 128) {                  // queries: rows beyond the tile are zero
+        const int r = i / kp8, piece = i % kp8;
+        cp_async16(Qs + r * qrow + piece * 8, r < rows ? q + (size_t)(tok0 + r) * q_stride + (size_t)h * dk + piece * 8 : q, r < rows);
+    }
+    stage(j_first, 0);
+
+    const int r0 = warp * 16 + (lane >> 2);                      // this thread's rows: r0 and r0 + 8 of the tile
+    const int qp0 = pos0 + r0, qp1 = qp0 + 8;
+    const float qf0 = a.scale * LOG2E * ((a.q_scale && r0 < rows) ? a.q_scale[qp0] : 1.0f);
+    const float qf1 = a.scale * LOG2E * ((a.q_scale && r0 + 8 < rows) ? a.q_scale[qp1] : 1.0f);
+    constexpr int NO = MMAX / 8;
+    float o[NO][4];
+#pragma unroll
+    for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int nvt = dv / 8;
+
+    for (int j = j_first; j <= j_last; ++j) {
+        const int buf = (j - j_first) & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                         // tile j is in; the other buffer is free
+        if (j < j_last) stage(j + 1, buf ^ 1);
+        const bf* kt = Ks + buf * MK * krow;
+        const bf* vt = Vs + buf * MK * vrow;
+        const float* bs = Bs + buf * (MQ + MK);
+        if (j * MK > pos0 + warp * 16 + 15) continue;            // every key of the tile lies after this warp's rows (uniform per warp)
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        for (int k0 = 0; k0 < dk; k0 += 16) {
+            uint32_t af[4];
+            ldsm_x4(af, Qs + (warp * 16 + (lane & 15)) * qrow + k0 + (lane >> 4) * 8);
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                uint32_t bfr[2];
+                ldsm_x2(bfr, kt + (n * 8 + (lane & 7)) * krow + k0 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[n], af, bfr);
+            }
+        }
+        // factor, bias, mask; row maxima.  Scores are kept in units of ln 2 (the factor and the staged bias carry
+        // log2 e), so that the exponentials are exp2.  A tile that every row of the warp sees whole needs no mask.
+        const int dist0 = pos0 - (j * MK + MK - 1);
+        const int w_lo = pos0 + warp * 16, w_hi = w_lo + 15;
+        const bool whole = j * MK + MK - 1 <= w_lo && w_hi <= pos_max && (a.window <= 0 || j * MK > w_hi - a.window);
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (whole) {
+            const float* b0 = bs + (qp0 - j * MK - dist0) - 2 * (lane & 3);      // bias of (row r0, key j*MK + 2*(lane&3)); keys go down
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                float x0 = s[n][0] * qf0, x1 = s[n][1] * qf0, x2 = s[n][2] * qf1, x3 = s[n][3] * qf1;
+                if (brow) {
+                    x0 += b0[-n * 8]; x1 += b0[-n * 8 - 1]; x2 += b0[-n * 8 + 8]; x3 += b0[-n * 8 + 7];
+                }
+                s[n][0] = x0; s[n][1] = x1; s[n][2] = x2; s[n][3] = x3;
+                mx0 = fmaxf(mx0, fmaxf(x0, x1));
+                mx1 = fmaxf(mx1, fmaxf(x2, x3));
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kp = j * MK + n * 8 + 2 * (lane & 3) + (e & 1);
+                    const int qp = (e < 2) ? qp0 : qp1;
+                    const bool vis = kp <= qp && qp <= pos_max && (a.window <= 0 || kp > qp - a.window);
+                    float sc = s[n][e] * ((e < 2) ? qf0 : qf1);
+                    if (brow && vis) sc += bs[qp - kp - dist0];
+                    sc = vis ? sc : -INFINITY;
+                    s[n][e] = sc;
+                    if (e < 2) mx0 = fmaxf(mx0, sc); else mx1 = fmaxf(mx1, sc);
+                }
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+        m0 = mn0; m1 = mn1;
+        float rs0 = 0.f, rs1 = 0.f;
+        uint32_t phi[4][4], plo[4][4];                           // A fragments of p for the four 16-key steps
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float p0 = exp2f(s[n][0] - mu0), p1 = exp2f(s[n][1] - mu0), p2 = exp2f(s[n][2] - mu1), p3 = exp2f(s[n][3] - mu1);
+            rs0 += p0 + p1;
+            rs1 += p2 + p3;
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+            const int kk = n >> 1, half = (n & 1) * 2;
+            phi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+            phi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+            plo[kk][half] = pack_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
+            plo[kk][half + 1] = pack_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
+        }
+        l0 = l0 * al0 + rs0;                                     // per-thread part of the row sums; the quad meets at the end
+        l1 = l1 * al1 + rs1;
+#pragma unroll
+        for (int i = 0; i < NO; ++i) {
+            if (i < nvt) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int i = 0; i < NO; ++i) {
+                if (i < nvt) {
+                    uint32_t bfr[2];
+                    ldsm_x2_trans(bfr, vt + (kk * 16 + (lane & 15)) * vrow + i * 8);
+                    mma_bf16(o[i], phi[kk], bfr);
+                    mma_bf16(o[i], plo[kk], bfr);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = a.out_scale / l0, inv1 = a.out_scale / l1;
+#pragma unroll
+    for (int i = 0; i < NO; ++i) {
+        if (i < nvt) {
+            const int col = i * 8 + 2 * (lane & 3);
+            if (r0 < rows)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + r0) * out_stride + (size_t)h * dv + col) =
+                    __floats2bfloat162_rn(o[i][0] * inv0, o[i][1] * inv0);
+            if (r0 + 8 < rows)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + r0 + 8) * out_stride + (size_t)h * dv + col) =
+                    __floats2bfloat162_rn(o[i][2] * inv1, o[i][3] * inv1);
+        }
+    }
+}
+
 int check_sizes(int H, int Hkv, int dk, int dv, int page_size, int dtype) {
     const int vec = dtype == MLLM_F32 ? 4 : 8;
     if (dtype != MLLM_F32 && dtype != MLLM_BF16) return mllm_fail(1, "attention_bias: unknown dtype code %d", dtype);
@@ -525,7 +747,8 @@ int check_sizes(int H, int Hkv, int dk, int dv, int page_size, int dtype) {
 
 MLLM_EXPORT int mllm_attention_bias_split_keys() { return SPLIT; }
 
-// impl: 0 simt, 1 tiled (needs tiles), 2 split (single tokens; needs part_o [T*H*nsplit*dv], part_ml [T*H*nsplit*2]).
+// impl: 0 simt, 1 tiled (needs tiles), 2 split (single tokens; needs part_o [T*H*nsplit*dv], part_ml [T*H*nsplit*2]),
+// 3 mma (bfloat16 prompt portions on tensor cores; needs tiles).
 MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                     const int* block_table, int bt_stride, const int* token_seq, const int* positions,
                                     const int* tiles, int n_tiles, void* out, long long out_stride, float* part_o,
@@ -599,6 +822,21 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                   (const float*)part_o, (const float*)part_ml, positions, (bf*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
         }
+        return 0;
+    }
+    if (impl == 3) {
+        if (!tiles || n_tiles <= 0) return mllm_fail(1, "attention_bias: the tensor-core kernel needs the step's tile list");
+        if (dtype != MLLM_BF16 || dk % 16 != 0 || dv % 16 != 0 || dk > MMAX || dv > MMAX || out_stride % 2 != 0 ||
+            (uintptr_t)out % 4 != 0 || (uintptr_t)k_pages % 16 != 0 || (uintptr_t)v_pages % 16 != 0 || (uintptr_t)q % 16 != 0 ||
+            q_stride % 8 != 0)
+            return mllm_fail(1, "attention_bias: the tensor-core kernel takes bfloat16, key and value sizes that are multiples "
+                                "of 16 up to %d and 16-byte aligned rows (got %d / %d)", MMAX, dk, dv);
+        const size_t smem = sizeof(bf) * ((size_t)MQ * (dk + 8) + 2 * (size_t)MK * (dk + 8) + 2 * (size_t)MK * (dv + 8)) +
+                            sizeof(float) * 2 * (MQ + MK);
+        MLLM_CUDA(cudaFuncSetAttribute(attention_bias_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MLLM_CUDA(mllm_launch(attention_bias_mma_kernel, dim3(H, n_tiles), dim3(128), smem, stream, true, (const bf*)q, q_stride,
+                              (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions, (bf*)out,
+                              out_stride, H, Hkv, dk, dv, page_size, a));
         return 0;
     }
     return mllm_fail(1, "attention_bias: unknown implementation %d", impl);

@@ -153,26 +153,48 @@ gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restri
     const int VPT = (WCH * WC + nthreads - 1) / nthreads;       // at most WVMAX when G >= 32 / WVMAX
     const bool ahead = VPT <= WVMAX;
     float av[WLD], zv[WLD], vv_next[WVMAX];
+    // where this thread's elements of a chunk lie, relative to the chunk's first token: the same in every chunk
+    int a_off[WLD], z_off[WLD], v_off[WVMAX];                  // at most 32 rows of the step ahead: they fit an int
+    int a_tok[WLD], v_tok[WVMAX];
+#pragma unroll
+    for (int u = 0; u < WLD; ++u) {
+        const int idx = tid + u * nthreads, c = idx / ekp, i = idx % ekp;
+        a_tok[u] = i < ek ? c : WCH;                             // WCH: never fetched (padding row)
+        a_off[u] = (int)(c * r.a_stride) + h * ek + i;
+        z_off[u] = (int)(c * r.z_stride) + h * ek + i;
+    }
+#pragma unroll
+    for (int u = 0; u < WVMAX; ++u) {
+        const int idx = tid + u * nthreads, c = idx / WC, d = idx % WC;
+        v_tok[u] = (u < VPT && j0 + d < ev) ? c : WCH;
+        v_off[u] = (int)(c * r.v_stride) + h * ev + j0 + d;
+    }
     auto fetch = [&](int c0) {
         const int n = min(WCH, t1 - c0);
+        const T* ab = a + (size_t)c0 * r.a_stride;
+        const T* zb = z + (size_t)c0 * r.z_stride;
+        const T* vb = v + (size_t)c0 * r.v_stride;
 #pragma unroll
         for (int u = 0; u < WLD; ++u) {
-            const int idx = tid + u * nthreads, c = idx / ekp, i = idx % ekp;
             av[u] = zv[u] = 0.f;
-            if (idx < n * ekp && i < ek) {
-                av[u] = to_f32(a[(size_t)(c0 + c) * r.a_stride + (size_t)h * ek + i]);
-                zv[u] = to_f32(z[(size_t)(c0 + c) * r.z_stride + (size_t)h * ek + i]);
+            if (a_tok[u] < n) {
+                av[u] = to_f32(ab[a_off[u]]);
+                zv[u] = to_f32(zb[z_off[u]]);
             }
         }
         if (ahead) {
 #pragma unroll
-            for (int u = 0; u < WVMAX; ++u) {
-                const int idx = tid + u * nthreads, c = idx / WC, d = idx % WC;
-                vv_next[u] = (u < VPT && idx < n * WC && j0 + d < ev)
-                                 ? to_f32(v[(size_t)(c0 + c) * r.v_stride + (size_t)h * ev + j0 + d]) : 0.f;
-            }
+            for (int u = 0; u < WVMAX; ++u) vv_next[u] = v_tok[u] < n ? to_f32(vb[v_off[u]]) : 0.f;
         }
     };
+    // the gate's bias and lower bound of this thread's elements: the same rows in every chunk
+    float lo_r[WLD], fb_r[WLD];
+#pragma unroll
+    for (int u = 0; u < WLD; ++u) {
+        const int i = (tid + u * nthreads) % ekp;
+        lo_r[u] = i < ek ? r.lower[h * ek + i] : 0.f;
+        fb_r[u] = i < ek ? r.f_bias[h * ek + i] : 0.f;
+    }
     if (t0 < t1) fetch(t0);
     for (int c0 = t0; c0 < t1; c0 += WCH) {
         const int n = min(WCH, t1 - c0);
@@ -183,9 +205,9 @@ gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restri
             if (idx >= n * ekp) continue;
             float qv = 0.f, fv = 1.f;
             if (i < ek) {
-                const float lo = r.lower[h * ek + i];
-                qv = av[u] / (1.0f + expf(-av[u]));
-                fv = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-(zv[u] + r.f_bias[h * ek + i]))));
+                const float lo = lo_r[u];
+                qv = av[u] * __frcp_rn(1.0f + expf(-av[u]));
+                fv = lo + (1.0f - lo) * __frcp_rn(1.0f + expf(-(zv[u] + fb_r[u])));
             }
             qs[idx] = qv;
             fs[idx] = fv;
@@ -213,7 +235,31 @@ gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restri
         }
         if (c0 + WCH < t1) fetch(c0 + WCH);   // the next chunk's loads are in flight during this chunk's walk
         __syncthreads();
-        for (int c = 0; c < n; ++c) {
+        // four tokens at a time: all twelve reads of shared memory first, then the arithmetic, then the four stores
+        // (in one loop the compiler keeps every read behind the store before it: it cannot tell the arrays apart)
+        int c = 0;
+        for (; c + 4 <= n; c += 4) {
+            float vv[4];
+            float4 f4[4], q4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                vv[u] = vs[(c + u) * WC + lane];
+                f4[u] = *reinterpret_cast<const float4*>(fs + (c + u) * ekp + g * WR);
+                q4[u] = *reinterpret_cast<const float4*>(qs + (c + u) * ekp + g * WR);
+            }
+            float ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                s[0] = fmaf(f4[u].x, s[0], (1.0f - f4[u].x) * vv[u]);
+                s[1] = fmaf(f4[u].y, s[1], (1.0f - f4[u].y) * vv[u]);
+                s[2] = fmaf(f4[u].z, s[2], (1.0f - f4[u].z) * vv[u]);
+                s[3] = fmaf(f4[u].w, s[3], (1.0f - f4[u].w) * vv[u]);
+                ov[u] = fmaf(s[3], q4[u].w, fmaf(s[2], q4[u].z, fmaf(s[1], q4[u].y, s[0] * q4[u].x)));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) os[(g * WCH + c + u) * WC + lane] = ov[u];
+        }
+        for (; c < n; ++c) {
             const float vv = vs[c * WC + lane];
             const float4 f4 = *reinterpret_cast<const float4*>(fs + c * ekp + g * WR);
             const float4 q4 = *reinterpret_cast<const float4*>(qs + c * ekp + g * WR);
@@ -227,6 +273,7 @@ gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restri
         for (int idx = tid; idx < n * WC; idx += nthreads) {          // row groups meet in group order
             const int c = idx / WC, d = idx % WC;
             float acc = os[c * WC + d];
+#pragma unroll 8
             for (int gg = 1; gg < G; ++gg) acc += os[(gg * WCH + c) * WC + d];
             if (j0 + d < ev) o[(size_t)(c0 + c) * o_stride + (size_t)h * ev + j0 + d] = acc;
         }

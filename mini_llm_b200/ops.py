@@ -730,6 +730,15 @@ def paged_write_kv(k, v, k_pages, v_pages, slot_mapping) -> None:
           v_pages.data_ptr(), slot_mapping.data_ptr(), T, heads, dk, dv, ps, _dt(k), _stream())
 
 
+BIAS_ATTN_MMA_MAX_DIM = 128    # largest key and value size of its tensor-core kernel
+
+
+def _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo) -> bool:
+    return (q.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and dk <= BIAS_ATTN_MMA_MAX_DIM
+            and dv <= BIAS_ATTN_MMA_MAX_DIM and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0
+            and out.data_ptr() % 4 == 0 and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0)
+
+
 BIAS_ATTN_MAX_DIM = 256        # largest key and value size of csrc/attention_bias.cu
 _bias_split_keys = None
 
@@ -777,6 +786,8 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
             impl = "split"
         elif getattr(ctx, "n_tiles", 0) > 0:
             impl = "tiled"
+            if q.dtype == torch.bfloat16 and _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo):
+                impl = "mma"       # prompt portions in bfloat16: tensor cores
     attention_launches["bias_" + impl] = attention_launches.get("bias_" + impl, 0) + 1
     part_o = part_ml = None
     nsplit = 0
@@ -789,8 +800,11 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
         nsplit = 1 << (need - 1).bit_length()
         part_o = ctx.ws.buf("battn_part_o", T * num_heads * nsplit, dv, torch.float32).data_ptr()
         part_ml = ctx.ws.buf("battn_part_ml", T * num_heads * nsplit, 2, torch.float32).data_ptr()
-    elif impl == "tiled":
+    elif impl in ("tiled", "mma"):
         tiles, n_tiles = ctx.attn_tiles.data_ptr(), int(ctx.n_tiles)
+        if impl == "mma" and not _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo):
+            raise KernelError("biased_attention: the tensor-core kernel takes bfloat16, key and value sizes that are "
+                              f"multiples of 16 up to {BIAS_ATTN_MMA_MAX_DIM} and 16-byte aligned rows")
     elif impl != "simt":
         raise KernelError(f"biased_attention: unknown implementation {impl!r}")
     _call("mllm_attention_bias", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
@@ -798,7 +812,7 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
           out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dk, dv, ps, float(scale),
           float(out_scale), dist_bias.data_ptr() if dist_bias is not None else None, n_dist,
           q_scale.data_ptr() if q_scale is not None else None, int(window or 0), _dt(q),
-          {"simt": 0, "tiled": 1, "split": 2}[impl], _stream())
+          {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl], _stream())
     if impl == "split":
         global launches
         launches += 1           # the kernel that merges the splits

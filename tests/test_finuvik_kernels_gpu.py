@@ -231,6 +231,22 @@ def test_distance_bias_attention_mixed_batch(ops, dtype, impl, H, G, dk, dv, pag
         assert (got - want).abs().max() < _tol(dtype) * 2 * max(1.0, want.abs().max().item()), (impl, kw)
 
 
+@pytest.mark.parametrize("H,G,dk,dv,page", [(3, 3, 32, 32, 16), (4, 2, 64, 128, 16), (2, 1, 128, 16, 8), (6, 2, 96, 48, 4),
+                                            (2, 2, 16, 16, 32)])
+def test_distance_bias_attention_on_tensor_cores(ops, H, G, dk, dv, page):
+    # the same mixed batch through the mma.sync kernel (bfloat16 only): against the oracle and against the tiled kernel
+    seqs = [(150, 97), (31, 31), (200, 1), (67, 2), (1, 1), (130, 65), (260, 129)]
+    case = _case(torch.bfloat16, seqs, H, G, dk, dv, page, seed=H * 100 + dk + 1)
+    for kw in (dict(), dict(use_bias=False), dict(use_qscale=False, out_scale=0.7), dict(window=37), dict(window=64)):
+        got, want = _run(ops, case, "mma", **kw), _want(case, **kw)
+        assert (got - want).abs().max() < _tol(torch.bfloat16) * 2 * max(1.0, want.abs().max().item()), kw
+    assert ops.attention_launches.get("bias_mma", 0) >= 5
+    # left to itself the wrapper takes this kernel for bfloat16 prompt portions of such sizes
+    before = ops.attention_launches.get("bias_mma", 0)
+    _run(ops, case, None)
+    assert ops.attention_launches["bias_mma"] == before + 1
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,page", SHAPES)
 def test_distance_bias_attention_single_tokens(ops, dtype, H, G, dk, dv, page):
@@ -245,22 +261,26 @@ def test_distance_bias_attention_single_tokens(ops, dtype, H, G, dk, dv, page):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("impl", ["simt", "tiled", "split"])
+@pytest.mark.parametrize("impl", ["simt", "tiled", "split", "mma"])
 def test_distance_bias_attention_finds_one_far_key_among_hundreds(ops, impl, dtype):
+    if impl == "mma" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernel is bfloat16 only")
     # the sharp key lies 600 and more positions back, in the first page; the bias takes about 3 off its score of
     # 45+, so it still carries the whole weight; its value row is 2.0 everywhere
     ql = 1 if impl == "split" else 40
     seqs = [(640, ql), (701, ql)]
-    case = _case(dtype, seqs, 4, 2, 32, 24, 16, seed=5, sharp={0: [3], 1: [16]}, r=(0.3, 0.1))
+    case = _case(dtype, seqs, 4, 2, 32, 32 if impl == "mma" else 24, 16, seed=5, sharp={0: [3], 1: [16]}, r=(0.3, 0.1))
     got, want = _run(ops, case, impl), _want(case)
     assert (got - want).abs().max() < _tol(dtype) * 2 * max(1.0, want.abs().max().item())
     assert (got - 2.0).abs().max() < 0.05          # nothing but the far key counts
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("impl", ["simt", "tiled", "split"])
+@pytest.mark.parametrize("impl", ["simt", "tiled", "split", "mma"])
 @pytest.mark.parametrize("window", [None, 48])
 def test_distance_bias_attention_edges_with_sharp_keys(ops, impl, dtype, window):
+    if impl == "mma" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernel is bfloat16 only")
     # sharp keys at the borders of pages (16), key chunks (32), tiles (64) and splits (256), at the first positions,
     # and (with a window) just inside and just outside the window of the queries near the end
     c = 330
