@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_bias_simt_kernel(const T* q, long long q_stride, const T* k_pages, const T* v_pages,
                            const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_seq,
                            const int* __restrict__ positions, T* __restrict__ out, long long out_stride, int T_tokens,
-                           int H, int Hkv, int dk, int dv, int page_size, BiasArgs a) {
+                           int H, int Hkv, int dkq, int dk, int dv, int page_size, BiasArgs a) {
     __shared__ float qs[WARPS][MAX_D];
     pdl_wait();
     pdl_launch();
@@ -109,8 +109,8 @@ attention_bias_simt_kernel(const T* q, long long q_stride, const T* k_pages, con
     const int hk = h / (H / Hkv);
     const int seq = token_seq[t], p = positions[t];
     const int* bt = block_table + (size_t)seq * bt_stride;
-    const T* qrow = q + (size_t)t * q_stride + (size_t)h * dk;
-    for (int d = lane; d < dk; d += 32) qs[warp][d] = to_f32(qrow[d]);
+    const T* qrow = q + (size_t)t * q_stride + (size_t)h * dkq;
+    for (int d = lane; d < dk; d += 32) qs[warp][d] = d < dkq ? to_f32(qrow[d]) : 0.f;     // key rows are padded with zeros
     __syncwarp();
     const float qf = a.scale * (a.q_scale ? a.q_scale[p] : 1.0f);
     int first = 0;
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(128)
 attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, const T* v_pages,
                             const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int H, int Hkv, int dk, int dv, int page_size, int HG, int KS, BiasArgs a) {
+                            int H, int Hkv, int dkq, int dk, int dv, int page_size, int HG, int KS, BiasArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int VEC = 16 / sizeof(T);
     const int krow = dk + VEC;                                  // elements per staged key row: 16 bytes of padding
@@ -176,7 +176,7 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
     const int* bt = block_table + (size_t)seq * bt_stride;
     for (int i = tid; i < HG * dk; i += nthreads) {
         const int hh = i / dk, d = i % dk;
-        qs[i] = hh < nh ? to_f32(q[(size_t)t * q_stride + (size_t)(h0 + hh) * dk + d]) : 0.f;
+        qs[i] = (hh < nh && d < dkq) ? to_f32(q[(size_t)t * q_stride + (size_t)(h0 + hh) * dkq + d]) : 0.f;
     }
     const float qf = a.scale * (a.q_scale ? a.q_scale[p] : 1.0f);
     const float* brow = (a.dist_bias && live) ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(THREADS)
 attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, const T* v_pages,
                             const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tiles,
                             const int* __restrict__ positions, T* __restrict__ out, long long out_stride, int H, int Hkv,
-                            int dk, int dv, int page_size, BiasArgs a) {
+                            int dkq, int dk, int dv, int page_size, BiasArgs a) {
     extern __shared__ float sm[];
     const int qrow = dk + 1;
     float* Qs = sm;                         // [BQ][dk+1]   queries times scale times their position's factor
@@ -378,9 +378,9 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
     for (int i = tid; i < BQ * dk; i += THREADS) {
         const int r = i / dk, d = i % dk;
         float v = 0.f;
-        if (r < rows) {
+        if (r < rows && d < dkq) {
             const float qf = a.scale * (a.q_scale ? a.q_scale[pos0 + r] : 1.0f);
-            v = to_f32(q[(size_t)(tok0 + r) * q_stride + (size_t)h * dk + d]) * qf;
+            v = to_f32(q[(size_t)(tok0 + r) * q_stride + (size_t)h * dkq + d]) * qf;
         }
         Qs[r * qrow + d] = v;
     }
@@ -752,11 +752,12 @@ MLLM_EXPORT int mllm_attention_bias_split_keys() { return SPLIT; }
 MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                     const int* block_table, int bt_stride, const int* token_seq, const int* positions,
                                     const int* tiles, int n_tiles, void* out, long long out_stride, float* part_o,
-                                    float* part_ml, int nsplit, int T, int H, int Hkv, int dk, int dv, int page_size,
+                                    float* part_ml, int nsplit, int T, int H, int Hkv, int dkq, int dk, int dv, int page_size,
                                     float scale, float out_scale, const float* dist_bias, int n_dist,
                                     const float* q_scale, int window, int dtype, int impl, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (int rc = check_sizes(H, Hkv, dk, dv, page_size, dtype)) return rc;
+    if (dkq <= 0 || dkq > dk) return mllm_fail(1, "attention_bias: queries of %d against key rows of %d", dkq, dk);
     BiasArgs a{dist_bias, n_dist, q_scale, scale, out_scale, window};
     const long long warps = (long long)T * H;
     const long long blocks = (warps + WARPS - 1) / WARPS;
@@ -766,12 +767,12 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
         if (dtype == MLLM_F32)
             MLLM_CUDA(mllm_launch(attention_bias_simt_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
                                   true, (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages,
-                                  block_table, bt_stride, token_seq, positions, (float*)out, out_stride, T, H, Hkv, dk, dv,
+                                  block_table, bt_stride, token_seq, positions, (float*)out, out_stride, T, H, Hkv, dkq, dk, dv,
                                   page_size, a));
         else
             MLLM_CUDA(mllm_launch(attention_bias_simt_kernel<bf>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride,
-                                  token_seq, positions, (bf*)out, out_stride, T, H, Hkv, dk, dv, page_size, a));
+                                  token_seq, positions, (bf*)out, out_stride, T, H, Hkv, dkq, dk, dv, page_size, a));
         return 0;
     }
     if (impl == 1) {
@@ -782,12 +783,12 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             MLLM_CUDA(cudaFuncSetAttribute(attention_bias_tiled_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_tiled_kernel<float>, dim3(H, n_tiles), dim3(THREADS), smem, stream, true,
                                   (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table,
-                                  bt_stride, tiles, positions, (float*)out, out_stride, H, Hkv, dk, dv, page_size, a));
+                                  bt_stride, tiles, positions, (float*)out, out_stride, H, Hkv, dkq, dk, dv, page_size, a));
         } else {
             MLLM_CUDA(cudaFuncSetAttribute(attention_bias_tiled_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_tiled_kernel<bf>, dim3(H, n_tiles), dim3(THREADS), smem, stream, true,
                                   (const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride,
-                                  tiles, positions, (bf*)out, out_stride, H, Hkv, dk, dv, page_size, a));
+                                  tiles, positions, (bf*)out, out_stride, H, Hkv, dkq, dk, dv, page_size, a));
         }
         return 0;
     }
@@ -809,7 +810,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_split_kernel<float>, grid, block, smem, stream, true,
                                   (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table,
-                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, HG, KS, a));
+                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (float*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
@@ -817,7 +818,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_split_kernel<bf>, grid, block, smem, stream, true,
                                   (const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride,
-                                  token_seq, positions, part_o, part_ml, H, Hkv, dk, dv, page_size, HG, KS, a));
+                                  token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<bf>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (bf*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
@@ -826,7 +827,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
     }
     if (impl == 3) {
         if (!tiles || n_tiles <= 0) return mllm_fail(1, "attention_bias: the tensor-core kernel needs the step's tile list");
-        if (dtype != MLLM_BF16 || dk % 16 != 0 || dv % 16 != 0 || dk > MMAX || dv > MMAX || out_stride % 2 != 0 ||
+        if (dtype != MLLM_BF16 || dkq != dk || dk % 16 != 0 || dv % 16 != 0 || dk > MMAX || dv > MMAX || out_stride % 2 != 0 ||
             (uintptr_t)out % 4 != 0 || (uintptr_t)k_pages % 16 != 0 || (uintptr_t)v_pages % 16 != 0 || (uintptr_t)q % 16 != 0 ||
             q_stride % 8 != 0)
             return mllm_fail(1, "attention_bias: the tensor-core kernel takes bfloat16, key and value sizes that are multiples "
@@ -862,12 +863,14 @@ paged_write_kernel(const T* src, long long row_stride, T* __restrict__ pages, co
 }
 }  // namespace
 
-// keys [T, heads * dk] and values [T, heads * dv] of the step to their page slots in one launch
+// keys [T, heads * dk] and values [T, heads * dv] of the step to their page slots in one launch; a key row of the
+// pages may be longer than dk (dkp, padded to a multiple of 8 so that rows stay 16-byte aligned): the padding is
+// never written and stays zero
 namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
 paged_write_kv_kernel(const T* k, long long k_stride, const T* v, long long v_stride, T* __restrict__ k_pages,
-                      T* __restrict__ v_pages, const int* __restrict__ slots, int T_tokens, int heads, int dk, int dv,
+                      T* __restrict__ v_pages, const int* __restrict__ slots, int T_tokens, int heads, int dk, int dkp, int dv,
                       int page_size) {
     pdl_wait();
     pdl_launch();
@@ -881,7 +884,7 @@ paged_write_kv_kernel(const T* k, long long k_stride, const T* v, long long v_st
         const int off = slot % page_size;
         if (c < pk) {
             const int h = c / dk, e = c % dk;
-            k_pages[((row + h) * page_size + off) * dk + e] = k[(size_t)t * k_stride + c];
+            k_pages[((row + h) * page_size + off) * dkp + e] = k[(size_t)t * k_stride + c];     // rows of dkp >= dk: the rest stays zero
         } else {
             const int cc = c - pk, h = cc / dv, e = cc % dv;
             v_pages[((row + h) * page_size + off) * dv + e] = v[(size_t)t * v_stride + cc];
@@ -891,18 +894,18 @@ paged_write_kv_kernel(const T* k, long long k_stride, const T* v, long long v_st
 }  // namespace
 
 MLLM_EXPORT int mllm_paged_write_kv(const void* k, long long k_stride, const void* v, long long v_stride, void* k_pages,
-                                    void* v_pages, const int* slots, int T, int heads, int dk, int dv, int page_size,
-                                    int dtype, cudaStream_t stream) {
+                                    void* v_pages, const int* slots, int T, int heads, int dk, int dkp, int dv,
+                                    int page_size, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     const long long total = (long long)T * heads * (dk + dv);
     const int grid = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(paged_write_kv_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)k, k_stride,
-                              (const float*)v, v_stride, (float*)k_pages, (float*)v_pages, slots, T, heads, dk, dv, page_size));
+                              (const float*)v, v_stride, (float*)k_pages, (float*)v_pages, slots, T, heads, dk, dkp, dv, page_size));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(paged_write_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
                               (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, (__nv_bfloat16*)k_pages,
-                              (__nv_bfloat16*)v_pages, slots, T, heads, dk, dv, page_size));
+                              (__nv_bfloat16*)v_pages, slots, T, heads, dk, dkp, dv, page_size));
     else
         return mllm_fail(1, "paged_write_kv: unknown dtype code %d", dtype);
     return 0;

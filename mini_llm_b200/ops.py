@@ -93,10 +93,10 @@ def _signatures(lib):
         "mllm_gated_act": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_paged_write": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_paged_write_kv": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                c_int, c_void_p],
+                                c_int, c_int, c_void_p],
         "mllm_attention_bias_split_keys": [],
         "mllm_attention_bias": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
@@ -713,21 +713,23 @@ def paged_write(src, pages, slot_mapping) -> None:
 
 def paged_write_kv(k, v, k_pages, v_pages, slot_mapping) -> None:
     """Keys k [T, heads * dk] and values v [T, heads * dv] (rows contiguous) to their slots in k_pages
-    [num_pages, heads, page_size, dk] and v_pages [num_pages, heads, page_size, dv], in one launch."""
+    [num_pages, heads, page_size, dkp] and v_pages [num_pages, heads, page_size, dv], in one launch.  dkp >= dk:
+    key rows of the pages may be padded (the padding is never written and stays zero)."""
     _cuda("k", k, contiguous=False)
     _cuda("v", v, k.dtype, contiguous=False)
     _cuda("k_pages", k_pages, k.dtype)
     _cuda("v_pages", v_pages, k.dtype)
     _cuda("slot_mapping", slot_mapping, torch.int32)
-    _, heads, ps, dk = k_pages.shape
+    _, heads, ps, dkp = k_pages.shape
     dv = v_pages.shape[3]
     T = k.shape[0]
-    if tuple(k.shape) != (T, heads * dk) or tuple(v.shape) != (T, heads * dv) or slot_mapping.numel() != T \
+    dk = k.shape[1] // heads
+    if k.shape[1] != heads * dk or dk > dkp or tuple(v.shape) != (T, heads * dv) or slot_mapping.numel() != T \
             or v_pages.shape[:3] != k_pages.shape[:3]:
         raise KernelError(f"paged_write_kv: k {tuple(k.shape)}, v {tuple(v.shape)} against pages {tuple(k_pages.shape)}, "
                           f"{tuple(v_pages.shape)}")
     _call("mllm_paged_write_kv", k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v), k_pages.data_ptr(),
-          v_pages.data_ptr(), slot_mapping.data_ptr(), T, heads, dk, dv, ps, _dt(k), _stream())
+          v_pages.data_ptr(), slot_mapping.data_ptr(), T, heads, dk, dkp, dv, ps, _dt(k), _stream())
 
 
 BIAS_ATTN_MMA_MAX_DIM = 128    # largest key and value size of its tensor-core kernel
@@ -749,8 +751,9 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
     ``dist_bias[head, i - j]`` (float32 [heads, n]) and a factor ``q_scale[position]`` (float32 [n]) on the query:
     out[t] = out_scale * softmax_j((q_t . k_j) * scale * q_scale[p_t] + dist_bias[h, p_t - j]) v_j.
 
-    q [T, heads * dk], k_pages [P, kv_heads, page_size, dk], v_pages [P, kv_heads, page_size, dv],
-    out [T, heads * dv] (rows contiguous; a column slice of a wider buffer is fine).
+    q [T, heads * dkq], k_pages [P, kv_heads, page_size, dk] with dk >= dkq a multiple of 8 (key rows padded with
+    zeros), v_pages [P, kv_heads, page_size, dv], out [T, heads * dv] (rows contiguous; a column slice of a wider
+    buffer is fine).
     """
     global _bias_split_keys
     _cuda("q", q, contiguous=False)
@@ -761,13 +764,14 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
     T = q.shape[0]
     _, Hkv, ps, dk = k_pages.shape
     dv = v_pages.shape[3]
-    if Hkv != num_kv_heads or q.shape[1] != num_heads * dk or tuple(out.shape) != (T, num_heads * dv) \
+    dkq = q.shape[1] // num_heads
+    if Hkv != num_kv_heads or q.shape[1] != num_heads * dkq or not (0 < dkq <= dk) or tuple(out.shape) != (T, num_heads * dv) \
             or v_pages.shape[:3] != k_pages.shape[:3]:
         raise KernelError("biased_attention: head counts or sizes do not fit the pages")
     ldq, ldo = _rows("q", q), _rows("out", out)
-    vec = 16 // q.element_size()
-    if dk % 8 != 0 or ldq % vec != 0 or q.data_ptr() % 16 != 0:
-        raise KernelError(f"biased_attention: key size {dk} must be a multiple of 8 and query rows 16-byte aligned")
+    if dk % 8 != 0 or dk > BIAS_ATTN_MAX_DIM or dv > BIAS_ATTN_MAX_DIM:
+        raise KernelError(f"biased_attention: key rows of {dk} must be a multiple of 8, and key and value rows at most "
+                          f"{BIAS_ATTN_MAX_DIM}")
     n_dist = 0
     if dist_bias is not None:
         _cuda("dist_bias", dist_bias, torch.float32)
@@ -786,7 +790,7 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
             impl = "split"
         elif getattr(ctx, "n_tiles", 0) > 0:
             impl = "tiled"
-            if q.dtype == torch.bfloat16 and _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo):
+            if dkq == dk and _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo):
                 impl = "mma"       # prompt portions in bfloat16: tensor cores
     attention_launches["bias_" + impl] = attention_launches.get("bias_" + impl, 0) + 1
     part_o = part_ml = None
@@ -802,14 +806,14 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
         part_ml = ctx.ws.buf("battn_part_ml", T * num_heads * nsplit, 2, torch.float32).data_ptr()
     elif impl in ("tiled", "mma"):
         tiles, n_tiles = ctx.attn_tiles.data_ptr(), int(ctx.n_tiles)
-        if impl == "mma" and not _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo):
+        if impl == "mma" and not (dkq == dk and _bias_mma_ok(q, k_pages, v_pages, out, dk, dv, ldq, ldo)):
             raise KernelError("biased_attention: the tensor-core kernel takes bfloat16, key and value sizes that are "
                               f"multiples of 16 up to {BIAS_ATTN_MMA_MAX_DIM} and 16-byte aligned rows")
     elif impl != "simt":
         raise KernelError(f"biased_attention: unknown implementation {impl!r}")
     _call("mllm_attention_bias", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
           _rows("block_table", block_table), ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), tiles, n_tiles,
-          out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dk, dv, ps, float(scale),
+          out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dkq, dk, dv, ps, float(scale),
           float(out_scale), dist_bias.data_ptr() if dist_bias is not None else None, n_dist,
           q_scale.data_ptr() if q_scale is not None else None, int(window or 0), _dt(q),
           {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl], _stream())

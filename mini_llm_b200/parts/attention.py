@@ -125,6 +125,7 @@ class DistanceBiasAttention(ProjectedMixer):
         self.q_size = self.num_heads * self.head_dim
         self.k_size = self.num_kv_heads * self.head_dim
         self.v_size = self.num_kv_heads * self.v_head_dim
+        self.k_row = -(-self.head_dim // 8) * 8        # a key row in the pages: padded to 16-byte pieces, the padding zero
         self.dist_bias = None
         self.q_scale = None
 
@@ -140,15 +141,15 @@ class DistanceBiasAttention(ProjectedMixer):
 
     def kernel_limits(self, dtype: str):
         out = []
-        if self.head_dim % 8 != 0 or not (8 <= self.head_dim <= 256):
-            out.append(f"distance-bias attention: key size {self.head_dim} is not a multiple of 8 between 8 and 256")
+        if not (1 <= self.head_dim <= 256):
+            out.append(f"distance-bias attention: key size {self.head_dim} is not between 1 and 256")
         if not (1 <= self.v_head_dim <= 256):
             out.append(f"distance-bias attention: value size {self.v_head_dim} is not between 1 and 256")
         return out
 
     def cache_need(self):
-        return PagedNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
-                         v_head_dim=None if self.v_head_dim == self.head_dim else self.v_head_dim)
+        return PagedNeed(kv_heads=self.num_kv_heads, head_dim=self.k_row, window=self.window,
+                         v_head_dim=None if self.v_head_dim == self.k_row else self.v_head_dim)
 
     def bind(self, params, rt) -> None:
         import torch

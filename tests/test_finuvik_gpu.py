@@ -316,10 +316,29 @@ def test_trace_replay_with_graphs(models, dtype, tmp_path):
         assert_close(np.concatenate(got[k]), want[k], dtype, f"replayed request {k}")
 
 
+def test_key_heads_whose_size_is_no_multiple_of_8(tmp_path):
+    """Key rows are padded in the pages (the padding stays zero); everything else takes the size as it is."""
+    from mini_llm_b200.engine.runner import StepEntry
+    cfg = _cfg(40, 50, 64, 1e-5, [_layer(2, 1, 12, 10, 1, 6, 9, 24, q_temp=(0.4, 4)), _layer(3, 3, 5, 5, 2, 3, 3, None)])
+    tensors = {k: v.to(torch.bfloat16).float() for k, v in make_tensors(cfg, 4).items()}
+    folder = write_model(str(tmp_path / "odd"), cfg, tensors)
+    ids = random_ids(50, cfg["vocab"], 9)
+    for dtype in ("float32", "bfloat16"):
+        want = oracle(tensors, cfg, ids, dtype)
+        from mini_llm_b200.config.base import EngineConfig
+        from mini_llm_b200.engine.runner import ModelRunner
+        r = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=8, num_pages=20, max_num_seqs=2, use_cuda_graphs=False))
+        r.add_request("a")
+        rows = [r.step([StepEntry("a", ids[:33], list(range(33)))]).cpu().numpy()]
+        for t in range(33, 50):
+            rows.append(r.step([StepEntry("a", [ids[t]], [0])]).cpu().numpy())
+        assert_close(np.concatenate(rows), want, dtype, "odd sizes")
+
+
 def test_sizes_no_kernel_takes_are_refused_at_construction(tmp_path):
     from mini_llm_b200.config.base import ConfigError, EngineConfig
     from mini_llm_b200.engine.runner import ModelRunner
-    cfg = _cfg(64, 50, 32, 1e-5, [_layer(2, 1, 12, 16, 1, 8, 8, 32)])        # key heads of 12: no multiple of 8
+    cfg = _cfg(64, 50, 32, 1e-5, [_layer(2, 1, 16, 16, 1, 256, 256, 32)])      # a state of 256 x 256 per head
     folder = write_model(str(tmp_path / "bad"), cfg, make_tensors(cfg, 0))
-    with pytest.raises(ConfigError, match="multiple of 8"):
+    with pytest.raises(ConfigError, match="threads"):
         ModelRunner(folder, EngineConfig(dtype="float32", num_pages=4))

@@ -109,19 +109,21 @@ def test_paged_write(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_paged_write_kv(ops, dtype):
-    T, heads, dk, dv, page, pages = 23, 2, 16, 5, 8, 7
+@pytest.mark.parametrize("dk,dkp", [(16, 16), (12, 16), (3, 8)])
+def test_paged_write_kv(ops, dtype, dk, dkp):
+    T, heads, dv, page, pages = 23, 2, 5, 8, 7
     wide = rnd(T, heads * (dk + dv) + 3, seed=8, dtype=dtype)
     k, v = wide[:, 3:3 + heads * dk], wide[:, 3 + heads * dk:]
-    kp = torch.zeros(pages, heads, page, dk, device=DEV, dtype=dtype)
+    kp = torch.zeros(pages, heads, page, dkp, device=DEV, dtype=dtype)
     vp = torch.zeros(pages, heads, page, dv, device=DEV, dtype=dtype)
     g = torch.Generator().manual_seed(10)
     slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32).to(DEV)
     ops.paged_write_kv(k, v, kp, vp, slots)
     for t in range(T):
         s = int(slots[t])
-        assert torch.equal(kp[s // page, :, s % page].reshape(-1), k[t])
+        assert torch.equal(kp[s // page, :, s % page, :dk].reshape(-1), k[t])
         assert torch.equal(vp[s // page, :, s % page].reshape(-1), v[t])
+    assert torch.all(kp[..., dk:] == 0)
 
 
 # ------------------------------------------------------------------------------------------------ attention
@@ -138,7 +140,7 @@ def _case(dtype, seqs, H, G, dk, dv, page, seed, sharp=None, r=(0.5, 0.2)):
     g = torch.Generator().manual_seed(seed)
     num_pages = sum((c + page - 1) // page for c, _ in seqs) + 3
     perm = torch.randperm(num_pages, generator=g).tolist()
-    k_pages = torch.zeros(num_pages, G, page, dk)
+    k_pages = torch.zeros(num_pages, G, page, -(-dk // 8) * 8)      # key rows padded to a multiple of 8, the padding zero
     v_pages = torch.zeros(num_pages, G, page, dv)
     tables, dense, token_seq, positions = [], [], [], []
     for s, (c, ql) in enumerate(seqs):
@@ -163,7 +165,7 @@ def _case(dtype, seqs, H, G, dk, dv, page, seed, sharp=None, r=(0.5, 0.2)):
     for s, tab in enumerate(tables):
         K, V = dense[s]
         for p in range(K.shape[0]):
-            k_pages[tab[p // page], :, p % page] = K[p]
+            k_pages[tab[p // page], :, p % page, :dk] = K[p]
             v_pages[tab[p // page], :, p % page] = V[p]
     mp = max(len(t) for t in tables)
     bt = torch.zeros(len(seqs), mp, dtype=torch.int32)
@@ -216,7 +218,8 @@ def _run(ops, case, impl, window=None, use_bias=True, use_qscale=True, out_scale
     return out.double().cpu()
 
 
-SHAPES = [(4, 2, 16, 24, 8), (3, 3, 32, 32, 16), (6, 1, 96, 40, 4), (2, 2, 8, 1, 16), (8, 2, 64, 256, 32), (1, 1, 256, 8, 16)]
+SHAPES = [(4, 2, 16, 24, 8), (3, 3, 32, 32, 16), (6, 1, 96, 40, 4), (2, 2, 8, 1, 16), (8, 2, 64, 256, 32), (1, 1, 256, 8, 16),
+          (4, 2, 12, 20, 8), (2, 1, 50, 7, 16)]          # the last two: key sizes that are no multiple of 8
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -311,9 +314,11 @@ def test_distance_bias_attention_result_does_not_depend_on_the_batch(ops):
 
 def test_distance_bias_attention_refuses_sizes_it_cannot_take(ops):
     case = _case(torch.float32, [(20, 5)], 2, 1, 16, 16, 8, seed=1)
-    bad_q = torch.zeros(5, 2 * 12, device=DEV)
-    with pytest.raises(ops.KernelError):
-        ops.biased_attention(bad_q, case["k_pages"][..., :12].contiguous(), case["v_pages"], case["bt"], case["ctx"],
+    with pytest.raises(ops.KernelError):      # key rows of the pages that are no multiple of 8
+        ops.biased_attention(torch.zeros(5, 2 * 12, device=DEV), case["k_pages"][..., :12].contiguous(), case["v_pages"],
+                             case["bt"], case["ctx"], torch.zeros(5, 32, device=DEV), num_heads=2, num_kv_heads=1, scale=1.0)
+    with pytest.raises(ops.KernelError):      # queries longer than the key rows
+        ops.biased_attention(torch.zeros(5, 2 * 24, device=DEV), case["k_pages"], case["v_pages"], case["bt"], case["ctx"],
                              torch.zeros(5, 32, device=DEV), num_heads=2, num_kv_heads=1, scale=1.0)
     with pytest.raises(ops.KernelError):      # a context beyond the bias table
         ops.biased_attention(case["q"], case["k_pages"], case["v_pages"], case["bt"], case["ctx"],
