@@ -135,21 +135,22 @@ constexpr int SPLIT = 256;          // keys per split
 
 // Single tokens.  grid (splits, kv heads x head chunks, tokens).  A CTA takes one split of one token's keys for HG
 // (1, 2 or 4) query heads that share a key/value head, so a key or value row is fetched once for all of them.  The
-// split is walked in tiles of 32 * KS keys (KS = 4 / HG key sub-tiles) that are staged in shared memory with 16-byte
-// loads (all loads of a burst before any store); warp w takes head w % HG and sub-tile w / HG: its lanes are the 32
-// keys for the scores (a row of K per lane, the query broadcast) and 32 value columns at a time for the weighted sum.
-// Sub-tile k of tile i covers the absolute positions [split*256 + (i*KS + k)*32, +32): chunks of 32 from position 0.
+// split is walked in tiles of 32 * KS * NT keys (KS = 4 / HG warps per head; NT chunks per warp: the whole split at once
+// where shared memory allows) that are staged in shared memory with 16-byte loads (all loads of a burst before any
+// store); warp w takes head w % HG and the chunks w / HG, w / HG + KS, ...: its lanes are the 32 keys for the scores (a
+// row of K per lane, the query broadcast) and 32 value columns at a time for the weighted sum.  Chunks cover 32
+// consecutive positions starting at multiples of 32 from position 0.
 // Partial results: part_o [T][H][splits][dv], part_ml [T][H][splits][2]; a split without visible keys writes l = 0.
 template <typename T>
 __global__ void __launch_bounds__(128)
 attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, const T* v_pages,
                             const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int H, int Hkv, int dkq, int dk, int dv, int page_size, int HG, int KS, BiasArgs a) {
+                            int H, int Hkv, int dkq, int dk, int dv, int page_size, int HG, int KS, int NT, BiasArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int VEC = 16 / sizeof(T);
     const int krow = dk + VEC;                                  // elements per staged key row: 16 bytes of padding
-    const int tile = 32 * KS;
+    const int tile = 32 * KS * NT;                              // keys staged at a time: NT chunks of 32 per warp
     T* Ks = reinterpret_cast<T*>(smraw);                        // [tile][dk + VEC]
     T* Vs = Ks + (size_t)tile * krow;                           // [tile][dv]
     float* qs = reinterpret_cast<float*>(Vs + (((size_t)tile * dv + VEC - 1) / VEC) * VEC);   // [HG][dk]
@@ -232,11 +233,13 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
             }
         }
         __syncthreads();
-        const int c0 = base + wk * 32;                          // this warp's 32 keys
+        for (int it = 0; it < NT; ++it) {
+        const int ck = (it * KS + wk) * 32;                     // this warp's chunk of 32 keys within the tile
+        const int c0 = base + ck;
         if (!live || c0 > s_hi || c0 + 31 < s_lo) continue;     // uniform over the warp (barriers are outside)
         const int kp = c0 + lane;
         const bool valid = kp >= s_lo && kp <= s_hi;
-        const T* kr = Ks + (size_t)(wk * 32 + lane) * krow;
+        const T* kr = Ks + (size_t)(ck + lane) * krow;
         const float* qh = qs + wh * dk;
         float dot = 0.f;
         for (int d = 0; d < dk; d += VEC) {
@@ -262,7 +265,7 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
         m = m_new;
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
-        const T* vt = Vs + (size_t)(wk * 32) * dv;
+        const T* vt = Vs + (size_t)ck * dv;
 #pragma unroll 4
         for (int j = 0; j < 32; ++j) {
             const float pj = __shfl_sync(0xffffffffu, pr, j);
@@ -271,6 +274,7 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
                 const int d = lane + 32 * i;
                 if (d < dv) acc[i] = fmaf(pj, to_f32(vt[(size_t)j * dv + d]), acc[i]);
             }
+        }
         }
     }
     __syncthreads();
@@ -797,12 +801,14 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
         const int R = H / Hkv;
         int HG = R >= 4 ? 4 : (R >= 2 ? 2 : 1), KS = 4 / HG;
         const size_t es = dtype == MLLM_F32 ? 4 : 2, vec = 16 / es;
-        auto bytes = [&](int ks) {
+        auto bytes = [&](int ks) {                               // ks: chunks of 32 keys staged at a time
             const size_t tile = 32 * (size_t)ks;
             return tile * (dk + vec) * es + ((tile * dv + vec - 1) / vec) * vec * es + sizeof(float) * ((size_t)HG * dk + 4 * (size_t)dv + 8);
         };
         while (KS > 1 && bytes(KS) > 96 * 1024) KS /= 2;
-        const size_t smem = bytes(KS);
+        int NT = 1;                                              // a whole split of 256 keys at a time where it fits
+        while (32 * KS * NT * 2 <= SPLIT && bytes(KS * NT * 2) <= 96 * 1024) NT *= 2;
+        const size_t smem = bytes(KS * NT);
         const int chunks = (R + HG - 1) / HG;
         if ((long long)Hkv * chunks > 65535 || T > 65535) return mllm_fail(1, "attention_bias: %d heads x %d tokens exceed the split kernel's grid", H, T);
         const dim3 grid(nsplit, Hkv * chunks, T), block(32 * HG * KS);
@@ -810,7 +816,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_split_kernel<float>, grid, block, smem, stream, true,
                                   (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table,
-                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, a));
+                                  bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, NT, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (float*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));
@@ -818,7 +824,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_split_kernel<bf>, grid, block, smem, stream, true,
                                   (const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride,
-                                  token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, a));
+                                  token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, NT, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<bf>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (bf*)out, out_stride, T, H, dv,
                                   nsplit, out_scale));

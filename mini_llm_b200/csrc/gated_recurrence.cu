@@ -15,8 +15,8 @@
 //
 // That kernel suits steps of single tokens, where reading and writing the state is all the work.  For prompt portions
 // a second kernel (`wide`) spreads one (request, head) over many more threads, since every element of the state is a
-// recurrence of its own: a CTA takes 32 columns of the state, thread (g, j) keeps rows 4g .. 4g+3 of column j, so a
-// token costs a thread four dependent fused multiply-adds instead of 64; the 32 tokens of a chunk are fetched into
+// recurrence of its own: a CTA takes 32 columns of the state, thread (g, j) keeps two or four rows of column j, so a
+// token costs a thread two or four dependent fused multiply-adds instead of 64; the 32 tokens of a chunk are fetched into
 // registers in one burst before anything is stored (loads and stores in one loop would be serialised, since the
 // compiler cannot tell the global inputs from shared memory), and the raw outputs o_t go to a 32-bit buffer that the
 // RMS norm kernel (csrc/rmsnorm.cu, one row per token and head) finishes.  Both kernels run the same recurrence per
@@ -118,14 +118,19 @@ gated_recurrence_kernel(const T* a, const T* z, const T* v, T* __restrict__ y, R
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int WR = 4;               // rows of the state a thread of the wide kernel keeps
+// rows of the state a thread of the wide kernel keeps: template parameter WR, 2 (states of up to 64 rows: twice the
+// warps to hide the walk's latencies) or 4 (up to 128 rows)
 constexpr int WC = 32;              // columns of the state a CTA of the wide kernel takes
 constexpr int WCH = 32;             // tokens per chunk
 constexpr int WLD = 4;              // elements of a and of z that a thread fetches per chunk (32 * 4G / 32G)
 constexpr int WVMAX = 8;            // elements of v a thread fetches ahead at most (32 / G of them: G >= 4)
 
 // grid (requests, heads, ceil(ev / 32)); block (32, G) with G = ceil(ek / 4) row groups.  o [T][Hr*ev] float.
-template <typename T>
+template <int WR> struct RowVec;
+template <> struct RowVec<2> { using type = float2; };
+template <> struct RowVec<4> { using type = float4; };
+
+template <typename T, int WR>
 __global__ void __launch_bounds__(1024)
 gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restrict__ o, long long o_stride, RecArgs r) {
     extern __shared__ __align__(16) float sm[];
@@ -237,37 +242,46 @@ gated_recurrence_wide_kernel(const T* a, const T* z, const T* v, float* __restri
         __syncthreads();
         // four tokens at a time: all twelve reads of shared memory first, then the arithmetic, then the four stores
         // (in one loop the compiler keeps every read behind the store before it: it cannot tell the arrays apart)
+        using RV = typename RowVec<WR>::type;
         int c = 0;
         for (; c + 4 <= n; c += 4) {
             float vv[4];
-            float4 f4[4], q4[4];
+            RV fr[4], qr[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 vv[u] = vs[(c + u) * WC + lane];
-                f4[u] = *reinterpret_cast<const float4*>(fs + (c + u) * ekp + g * WR);
-                q4[u] = *reinterpret_cast<const float4*>(qs + (c + u) * ekp + g * WR);
+                fr[u] = *reinterpret_cast<const RV*>(fs + (c + u) * ekp + g * WR);
+                qr[u] = *reinterpret_cast<const RV*>(qs + (c + u) * ekp + g * WR);
             }
             float ov[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                s[0] = fmaf(f4[u].x, s[0], (1.0f - f4[u].x) * vv[u]);
-                s[1] = fmaf(f4[u].y, s[1], (1.0f - f4[u].y) * vv[u]);
-                s[2] = fmaf(f4[u].z, s[2], (1.0f - f4[u].z) * vv[u]);
-                s[3] = fmaf(f4[u].w, s[3], (1.0f - f4[u].w) * vv[u]);
-                ov[u] = fmaf(s[3], q4[u].w, fmaf(s[2], q4[u].z, fmaf(s[1], q4[u].y, s[0] * q4[u].x)));
+                const float* f = reinterpret_cast<const float*>(&fr[u]);
+                const float* q = reinterpret_cast<const float*>(&qr[u]);
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < WR; ++i) {
+                    s[i] = fmaf(f[i], s[i], (1.0f - f[i]) * vv[u]);
+                    acc = fmaf(s[i], q[i], acc);
+                }
+                ov[u] = acc;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) os[(g * WCH + c + u) * WC + lane] = ov[u];
         }
         for (; c < n; ++c) {
             const float vv = vs[c * WC + lane];
-            const float4 f4 = *reinterpret_cast<const float4*>(fs + c * ekp + g * WR);
-            const float4 q4 = *reinterpret_cast<const float4*>(qs + c * ekp + g * WR);
-            s[0] = fmaf(f4.x, s[0], (1.0f - f4.x) * vv);
-            s[1] = fmaf(f4.y, s[1], (1.0f - f4.y) * vv);
-            s[2] = fmaf(f4.z, s[2], (1.0f - f4.z) * vv);
-            s[3] = fmaf(f4.w, s[3], (1.0f - f4.w) * vv);
-            os[(g * WCH + c) * WC + lane] = fmaf(s[3], q4.w, fmaf(s[2], q4.z, fmaf(s[1], q4.y, s[0] * q4.x)));
+            const RV fr = *reinterpret_cast<const RV*>(fs + c * ekp + g * WR);
+            const RV qr = *reinterpret_cast<const RV*>(qs + c * ekp + g * WR);
+            const float* f = reinterpret_cast<const float*>(&fr);
+            const float* q = reinterpret_cast<const float*>(&qr);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < WR; ++i) {
+                s[i] = fmaf(f[i], s[i], (1.0f - f[i]) * vv);
+                acc = fmaf(s[i], q[i], acc);
+            }
+            os[(g * WCH + c) * WC + lane] = acc;
         }
         __syncthreads();
         for (int idx = tid; idx < n * WC; idx += nthreads) {          // row groups meet in group order
@@ -294,6 +308,7 @@ MLLM_EXPORT int mllm_gated_recurrence_wide(const void* a, long long a_stride, co
                                            int S, int Hr, int ek, int ev, int write_state, int dtype, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (ek <= 0 || ev <= 0 || Hr <= 0) return mllm_fail(1, "gated_recurrence: sizes %d x %d x %d", Hr, ek, ev);
+    const int WR = ek <= 64 ? 2 : 4;      // measured at 32 rows: 171 us with 2 rows per thread, 190 with 1, 240 with 4
     const int G = (ek + WR - 1) / WR;
     if (G > 32) return mllm_fail(1, "gated_recurrence: the wide kernel takes states of up to %d rows, not %d", 32 * WR, ek);
     if (Hr > 65535 || (ev + WC - 1) / WC > 65535) return mllm_fail(1, "gated_recurrence: sizes exceed the grid");
@@ -302,14 +317,17 @@ MLLM_EXPORT int mllm_gated_recurrence_wide(const void* a, long long a_stride, co
               Hr, ek, ev, 0, G, WCH, write_state, 0.f, 1.f};
     const dim3 grid(S, Hr, (ev + WC - 1) / WC), block(32, G);
     using bf = __nv_bfloat16;
+#define MLLM_WIDE(TT, RR)                                                                                              \
+    do {                                                                                                               \
+        MLLM_CUDA(cudaFuncSetAttribute(gated_recurrence_wide_kernel<TT, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       (int)smem));                                                                    \
+        MLLM_CUDA(mllm_launch(gated_recurrence_wide_kernel<TT, RR>, grid, block, smem, stream, true, (const TT*)a,      \
+                              (const TT*)z, (const TT*)v, o, o_stride, r));                                            \
+    } while (0)
     if (dtype == MLLM_F32) {
-        MLLM_CUDA(cudaFuncSetAttribute(gated_recurrence_wide_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        MLLM_CUDA(mllm_launch(gated_recurrence_wide_kernel<float>, grid, block, smem, stream, true, (const float*)a,
-                              (const float*)z, (const float*)v, o, o_stride, r));
+        if (WR == 2) MLLM_WIDE(float, 2); else MLLM_WIDE(float, 4);
     } else if (dtype == MLLM_BF16) {
-        MLLM_CUDA(cudaFuncSetAttribute(gated_recurrence_wide_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        MLLM_CUDA(mllm_launch(gated_recurrence_wide_kernel<bf>, grid, block, smem, stream, true, (const bf*)a, (const bf*)z,
-                              (const bf*)v, o, o_stride, r));
+        if (WR == 2) MLLM_WIDE(bf, 2); else MLLM_WIDE(bf, 4);
     } else {
         return mllm_fail(1, "gated_recurrence: unknown dtype code %d", dtype);
     }
