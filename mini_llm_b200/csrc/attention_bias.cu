@@ -519,7 +519,7 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
 // a warp owns 16 query rows.  Key tile j covers the absolute positions [64j, 64j + 64).  Keys and values come into
 // shared memory by cp.async (rows nobody sees are zero-filled), the next tile's while the current one is used.
 // S = Q K^T is accumulated in 32-bit; the query's factor, the scale and the distance bias are applied to the 32-bit
-// sums; the online softmax is 32-bit (scores in units of ln 2 and exp2f); the weights go into the second product as p = hi + lo, two bfloat16
+// sums; the online softmax is 32-bit (scores in units of ln 2 and ex2.approx); the weights go into the second product as p = hi + lo, two bfloat16
 // terms, so that they keep about 16 bits; the output sums are 32-bit.
 constexpr int MQ = 64, MK = 64, MMAX = 128;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -550,6 +550,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float ex2(float x) {                   // 2^x in one instruction; 2^(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// NO: value tiles of 8 columns the kernel is compiled for (4, 8 or 16: value sizes up to 32, 64, 128)
+template <int NO>
 __global__ void __launch_bounds__(128)
 attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages,
                           const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tiles,
@@ -611,7 +619,6 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
     const int qp0 = pos0 + r0, qp1 = qp0 + 8;
     const float qf0 = a.scale * LOG2E * ((a.q_scale && r0 < rows) ? a.q_scale[qp0] : 1.0f);
     const float qf1 = a.scale * LOG2E * ((a.q_scale && r0 + 8 < rows) ? a.q_scale[qp1] : 1.0f);
-    constexpr int NO = MMAX / 8;
     float o[NO][4];
 #pragma unroll
     for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -680,13 +687,13 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+        const float al0 = ex2(m0 - mu0), al1 = ex2(m1 - mu1);
         m0 = mn0; m1 = mn1;
         float rs0 = 0.f, rs1 = 0.f;
         uint32_t phi[4][4], plo[4][4];                           // A fragments of p for the four 16-key steps
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
-            const float p0 = exp2f(s[n][0] - mu0), p1 = exp2f(s[n][1] - mu0), p2 = exp2f(s[n][2] - mu1), p3 = exp2f(s[n][3] - mu1);
+            const float p0 = ex2(s[n][0] - mu0), p1 = ex2(s[n][1] - mu0), p2 = ex2(s[n][2] - mu1), p3 = ex2(s[n][3] - mu1);
             rs0 += p0 + p1;
             rs1 += p2 + p3;
             const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
@@ -806,8 +813,19 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
             return tile * (dk + vec) * es + ((tile * dv + vec - 1) / vec) * vec * es + sizeof(float) * ((size_t)HG * dk + 4 * (size_t)dv + 8);
         };
         while (KS > 1 && bytes(KS) > 96 * 1024) KS /= 2;
-        int NT = 1;                                              // a whole split of 256 keys at a time where it fits
-        while (32 * KS * NT * 2 <= SPLIT && bytes(KS * NT * 2) <= 96 * 1024) NT *= 2;
+        // A whole split of 256 keys staged at once (one round of loads instead of up to eight) where it fits and the grid
+        // is small: with few CTAs nothing else hides the loads' latency.  In a large grid (measured at batch 64: 0.57
+        // against 0.71 ms per step) small tiles win, since more CTAs fit an SM and hide each other's loads.  A warp
+        // walks the same chunks in the same order either way, so the result is the same bits.
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            MLLM_CUDA(cudaGetDevice(&dev));
+            MLLM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        }
+        int NT = 1;
+        if ((long long)nsplit * Hkv * ((R + HG - 1) / HG) * T <= 4LL * sms)
+            while (32 * KS * NT * 2 <= SPLIT && bytes(KS * NT * 2) <= 96 * 1024) NT *= 2;
         const size_t smem = bytes(KS * NT);
         const int chunks = (R + HG - 1) / HG;
         if ((long long)Hkv * chunks > 65535 || T > 65535) return mllm_fail(1, "attention_bias: %d heads x %d tokens exceed the split kernel's grid", H, T);
@@ -840,10 +858,14 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                 "of 16 up to %d and 16-byte aligned rows (got %d / %d)", MMAX, dk, dv);
         const size_t smem = sizeof(bf) * ((size_t)MQ * (dk + 8) + 2 * (size_t)MK * (dk + 8) + 2 * (size_t)MK * (dv + 8)) +
                             sizeof(float) * 2 * (MQ + MK);
-        MLLM_CUDA(cudaFuncSetAttribute(attention_bias_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        MLLM_CUDA(mllm_launch(attention_bias_mma_kernel, dim3(H, n_tiles), dim3(128), smem, stream, true, (const bf*)q, q_stride,
-                              (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions, (bf*)out,
-                              out_stride, H, Hkv, dk, dv, page_size, a));
+#define MLLM_MMA(NN)                                                                                                   \
+    do {                                                                                                               \
+        MLLM_CUDA(cudaFuncSetAttribute(attention_bias_mma_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MLLM_CUDA(mllm_launch(attention_bias_mma_kernel<NN>, dim3(H, n_tiles), dim3(128), smem, stream, true, (const bf*)q,   \
+                              q_stride, (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions,     \
+                              (bf*)out, out_stride, H, Hkv, dk, dv, page_size, a));                                           \
+    } while (0)
+        if (dv <= 32) MLLM_MMA(4); else if (dv <= 64) MLLM_MMA(8); else MLLM_MMA(16);
         return 0;
     }
     return mllm_fail(1, "attention_bias: unknown implementation %d", impl);

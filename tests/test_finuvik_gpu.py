@@ -316,6 +316,40 @@ def test_trace_replay_with_graphs(models, dtype, tmp_path):
         assert_close(np.concatenate(got[k]), want[k], dtype, f"replayed request {k}")
 
 
+def test_command_line_with_random_weights_and_sampling(models, tmp_path):
+    """bin/mini_llm: the random-weights mode writes a Finuvik folder from a config.json; greedy tokens from the command
+    line equal LLM.generate's; temperature sampling gives the same tokens for the same seed and other tokens for another."""
+    import json
+    import subprocess
+    import sys
+    from helpers import ROOT
+    from mini_llm_b200 import LLM, SamplingParams
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(CFG_Y))
+    out_dir = tmp_path / "written"
+    cli = [sys.executable, os.path.join(ROOT, "bin", "mini_llm")]
+    r = subprocess.run(cli + ["--random-config", str(cfg_path), "--seed", "7", "--write-model", str(out_dir)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and os.path.isfile(out_dir / "model.safetensors"), r.stderr[-2000:]
+    prompts = ["5 17 3 90 9 100 4", "40 2 2 31"]
+    base = cli + ["--model", str(out_dir), "--dtype", "float32", "--max-new-tokens", "6", "--ignore-eos", "--max-batch-num", "2"]
+    for p in prompts:
+        base += ["--prompt-ids", p]
+    r = subprocess.run(base, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.endswith("[DONE]")]
+    got = [[int(t) for t in l.replace("[DONE]", "").split()] for l in lines]
+    llm = LLM(str(out_dir), dtype="float32", max_num_seqs=2)
+    want = llm.generate([[int(t) for t in p.split()] for p in prompts], SamplingParams(max_new_tokens=6, ignore_eos=True))
+    assert got == want
+    runs = []
+    for seed in ("3", "3", "4"):
+        r = subprocess.run(base + ["--temperature", "1.5", "--sample-seed", seed], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        runs.append(r.stdout)
+    assert runs[0] == runs[1] and runs[0] != runs[2]
+
+
 def test_key_heads_whose_size_is_no_multiple_of_8(tmp_path):
     """Key rows are padded in the pages (the padding stays zero); everything else takes the size as it is."""
     from mini_llm_b200.engine.runner import StepEntry

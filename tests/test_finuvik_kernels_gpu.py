@@ -312,6 +312,25 @@ def test_distance_bias_attention_result_does_not_depend_on_the_batch(ops):
     assert torch.equal(_run(ops, alone, "tiled"), got[:40])
 
 
+def test_decode_attention_in_a_large_batch_equals_the_small_batch_bit_for_bit(ops):
+    # 80 single tokens make a grid in which the split kernel stages small tiles; 5 of them alone make one in which it
+    # stages a whole split at once: the chunks a warp walks and their order are the same, so are the bits
+    H, G, dk, dv, page = 8, 2, 32, 48, 16
+    seqs = [(600 - 7 * i, 1) for i in range(80)]
+    big = _case(torch.float32, seqs, H, G, dk, dv, page, seed=21)
+    got = _run(ops, big, "split")
+    want = _want(big)
+    assert (got - want).abs().max() < _tol(torch.float32) * 2 * max(1.0, want.abs().max().item())
+    small = dict(big)
+    small["q"] = big["q"][:5].contiguous()
+    small["token_seq"], small["positions"] = big["token_seq"][:5], big["positions"][:5]
+    ctx = _Ctx()
+    ctx.token_seq, ctx.positions = big["ctx"].token_seq[:5].contiguous(), big["ctx"].positions[:5].contiguous()
+    ctx.ws, ctx.max_ctx_len, ctx.decode_only, ctx.n_tiles, ctx.attn_tiles = big["ctx"].ws, 600, True, 0, None
+    small["ctx"] = ctx
+    assert torch.equal(_run(ops, small, "split"), got[:5])
+
+
 def test_distance_bias_attention_refuses_sizes_it_cannot_take(ops):
     case = _case(torch.float32, [(20, 5)], 2, 1, 16, 16, 8, seed=1)
     with pytest.raises(ops.KernelError):      # key rows of the pages that are no multiple of 8
