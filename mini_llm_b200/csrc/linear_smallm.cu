@@ -47,6 +47,7 @@ struct NormArgs {
     const float* gamma;
     const float* beta;
     float eps;
+    int rms;                 // 1: no centring (an RMS norm: x / sqrt(mean(x^2) + eps) * gamma + beta)
 };
 // Fused cache write on the output of a Q|K|V projection: columns [0, q_size) go to q_out,
 // the key and value columns go straight to their page slots
@@ -154,7 +155,7 @@ linear_smallm_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat16*
                     s += (v.x + v.y) + (v.z + v.w);
                 }
             }
-            const float mean = warp_sum(s) / (float)K;
+            const float mean = ln.rms ? 0.f : warp_sum(s) / (float)K;
             float q = 0.f;
             if (fits) {
 #pragma unroll
@@ -399,7 +400,8 @@ MLLM_EXPORT int mllm_linear_smallm_fused(const void* x, long long ldx, const voi
                                          const float* beta, float eps, void* k_pages, void* v_pages,
                                          const int* slots, int q_size, int kv_heads, int head_dim, int page_size,
                                          cudaStream_t stream) {
-    NormArgs ln{norm_x, norm_rows, gamma, beta, eps};
+    // a negative eps asks for the norm without centring (RMS norm) with |eps|
+    NormArgs ln{norm_x, norm_rows, gamma, beta, fabsf(eps), eps < 0.f ? 1 : 0};
     KvArgs kv{(__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
     Call c{x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, norm_x ? &ln : nullptr, k_pages ? &kv : nullptr, stream};
     return dispatch(c, out_dtype);

@@ -52,6 +52,7 @@ struct LnArgs {
     const float* gamma;
     const float* beta;
     float eps;
+    int rms;                 // 1: no centring (an RMS norm: x / sqrt(mean(x^2) + eps) * gamma + beta)
 };
 struct KvArgs {
     float* k_pages;          // [page][kv_head][offset][head_dim]
@@ -189,7 +190,7 @@ linear_stream_f32_few_kernel(const float* x, long long ldx, const float* __restr
                 const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
                 sum += (v.x + v.y) + (v.z + v.w);
             }
-            const float mean = warp_sum(sum) / (float)K;
+            const float mean = ln.rms ? 0.f : warp_sum(sum) / (float)K;
             float var = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -513,7 +514,7 @@ linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __rest
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < KP; ++c) sum += (rv[c].x + rv[c].y) + (rv[c].z + rv[c].w);
-            const float mean = warp_sum(sum) / (float)K;
+            const float mean = ln.rms ? 0.f : warp_sum(sum) / (float)K;
             float var = 0.f;
 #pragma unroll
             for (int c = 0; c < KP; ++c) {
@@ -928,7 +929,8 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     if (kvw && (!v_pages || !slots || kv_heads <= 0 || head_dim <= 0 || page_size <= 0 ||
                 N != q_size + 2 * kv_heads * head_dim || accumulate))
         return mllm_fail(1, "linear_stream_f32: cache write arguments do not fit N=%d", N);
-    LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, ln_eps};
+    // a negative eps asks for the norm without centring (RMS norm) with |eps|
+    LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, fabsf(ln_eps), ln_eps < 0.f ? 1 : 0};
     KvArgs kv = {(float*)k_pages, (float*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
     const int tiles = (N + R - 1) / R;
     const int tall_rw = M <= tall_rows_for(N, K) ? tall_shape(N, K) : 0;

@@ -391,17 +391,28 @@ def gated_act(gu, out, act: str) -> None:
 # --------------------------------------------------------------------------- linear
 class NormedInput:
     """LayerNorm(x[rows]) not yet computed: a product that can fuse the norm into its
-    loads takes it as it is, anything else calls ``materialize()``."""
+    loads takes it as it is, anything else calls ``materialize()``.  ``rms``: the norm
+    without centring, x / sqrt(mean(x^2) + eps) * gamma (+ beta, which is then zeros);
+    ``buf``: the workspace buffer a materialised result goes to."""
 
-    def __init__(self, x, gamma, beta, eps, rows, ws, dtype):
+    def __init__(self, x, gamma, beta, eps, rows, ws, dtype, rms: bool = False, buf: str = "norm_out"):
         self.x, self.gamma, self.beta, self.eps, self.rows, self.ws, self.dtype = x, gamma, beta, eps, rows, ws, dtype
+        self.rms, self.buf = bool(rms), buf
         self.shape = (x.shape[0] if rows is None else rows.shape[0], x.shape[1])
         self._out = None
 
+    @property
+    def kernel_eps(self) -> float:
+        """eps as the fused products take it: negative for the norm without centring."""
+        return -float(self.eps) if self.rms else float(self.eps)
+
     def materialize(self):
         if self._out is None:
-            out = self.ws.buf("norm_out", self.shape[0], self.shape[1], self.dtype)
-            layernorm(self.x, self.gamma, self.beta, self.eps, out, rows=self.rows)
+            out = self.ws.buf(self.buf, self.shape[0], self.shape[1], self.dtype)
+            if self.rms:
+                rmsnorm(self.x, self.gamma, self.eps, out, rows=self.rows, unit_offset=False)
+            else:
+                layernorm(self.x, self.gamma, self.beta, self.eps, out, rows=self.rows)
             self._out = out
         return self._out
 
@@ -464,7 +475,7 @@ def _linear_fused(x, weight, bias, out, act, accumulate, norm: Optional[NormedIn
     if norm is not None:
         xp, ldx = None, norm.x.stride(0)
         nargs = (norm.x.data_ptr(), norm.rows.data_ptr() if norm.rows is not None else None,
-                 norm.gamma.data_ptr(), norm.beta.data_ptr(), float(norm.eps))
+                 norm.gamma.data_ptr(), norm.beta.data_ptr(), norm.kernel_eps)
     else:
         xp, ldx = x.data_ptr(), _rows("x", x)
         nargs = (None, None, None, None, 0.0)
@@ -501,7 +512,7 @@ def _linear_stream_f32(x, weight, bias, out, act, accumulate, norm: Optional[Nor
     if norm is not None:
         xp, ldx = None, norm.x.stride(0)
         nargs = (norm.x.data_ptr(), norm.rows.data_ptr() if norm.rows is not None else None,
-                 norm.gamma.data_ptr(), norm.beta.data_ptr(), float(norm.eps))
+                 norm.gamma.data_ptr(), norm.beta.data_ptr(), norm.kernel_eps)
     else:
         xp, ldx = x.data_ptr(), _rows("x", x)
         nargs = (None, None, None, None, 0.0)

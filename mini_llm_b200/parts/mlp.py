@@ -71,14 +71,23 @@ class GatedMLP(FeedForward):
             self.gate_weight = self.gate_up_weight[:self.inner_size]
             self.up_weight = self.gate_up_weight[self.inner_size:]
 
-    def forward(self, h, ctx, out_accum):
+    accepts_lazy_norm = True
+
+    def project(self, h, ctx):
+        """The first half: gate | up of h (a tensor or a norm not yet evaluated).  It only reads; an arrangement whose
+        branches all read the same x calls it before any branch adds to x."""
+        gu = ctx.ws.buf("ff_gate_up", h.shape[0], 2 * self.inner_size, self.rt.act_dtype)
+        self.rt.ops.linear(h, self.gate_up_weight, None, out=gu)
+        return gu
+
+    def finish(self, gu, ctx, out_accum):
         ops = self.rt.ops
-        T, F = h.shape[0], self.inner_size
-        gu = ctx.ws.buf("ff_gate_up", T, 2 * F, self.rt.act_dtype)
-        ops.linear(h, self.gate_up_weight, None, out=gu)
-        mid = ctx.ws.buf("ff_mid", T, F, self.rt.act_dtype)
+        mid = ctx.ws.buf("ff_mid", gu.shape[0], self.inner_size, self.rt.act_dtype)
         ops.gated_act(gu, mid, self.activation)
         ops.linear(mid, self.down_weight, None, out=out_accum, accumulate=True)
+
+    def forward(self, h, ctx, out_accum):
+        self.finish(self.project(h, ctx), ctx, out_accum)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -38,7 +38,10 @@ register_part("norm", "layernorm", LayerNorm)
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * (w + 1) for weights stored around zero (``unit_offset``), or * w for
     plain weights; eps inside the root, all 32-bit.  ``forward_pair`` norms the same rows with two weight
-    vectors (this norm's and ``other``'s) from one sum of squares: the two branches of a parallel block."""
+    vectors (this norm's and ``other``'s) from one sum of squares: the two branches of a parallel block.  With
+    ``lazy=True`` a product that can take the norm into its loads gets it unevaluated (few rows: decode steps)."""
+
+    supports_lazy = True
 
     def __init__(self, hidden_size: int, eps: float, unit_offset: bool = False):
         self.hidden_size = int(hidden_size)
@@ -48,7 +51,17 @@ class RMSNorm(Norm):
     def param_specs(self):
         return {"weight": ParamSpec((self.hidden_size,), "vector")}
 
+    def bind(self, params, rt) -> None:
+        import torch
+        super().bind(params, rt)
+        if "weight" in params:       # what the fused products multiply and add: w + 1 (or w), and nothing
+            self.gamma = (self.weight + 1.0).contiguous() if self.unit_offset else self.weight
+            self.zero_beta = torch.zeros_like(self.weight)
+
     def forward(self, x, ctx, rows=None, lazy=False, name="norm_out"):
+        if lazy:
+            return self.rt.ops.NormedInput(x, self.gamma, self.zero_beta, self.eps, rows, ctx.ws, self.rt.act_dtype,
+                                           rms=True, buf=name)
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buf(name, n, self.hidden_size, self.rt.act_dtype)
         self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows=rows, unit_offset=self.unit_offset)

@@ -24,6 +24,7 @@ from .base import Mixer, get_part_factory, register_part
 
 
 class ProjectedMixer(Mixer):
+    accepts_lazy_norm = True            # the first thing done with the input is a product
     in_names: Sequence[str] = ()        # parameters stacked (by rows) into the input projection, in this order
     out_name: str = "out_weight"        # the output projection [hidden, core_width]
 
@@ -58,6 +59,8 @@ class ProjectedMixer(Mixer):
 class ParallelMixer(Mixer):
     """``branches``: a list of {"name", "kind", "params"} (kind: a registered ProjectedMixer);
     ``scales``: the factor on each branch's result.  Parameters are named "<branch name>.<local name>"."""
+
+    accepts_lazy_norm = True
 
     def __init__(self, branches: List[Dict[str, Any]], scales: Sequence[float]):
         if len(branches) != len(scales) or not branches:

@@ -70,6 +70,41 @@ def test_rmsnorm(ops, out_dtype, R, D, eps):
     assert torch.equal(out2, one[rows.long()])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K,eps", [(1, 96, 64, 1e-5), (8, 1184, 768, 1e-6), (16, 200, 1600, 1e-5), (3, 4096, 2048, 1e-5),
+                                       (40, 64, 128, 1e-5)])
+def test_products_take_an_rms_norm_into_their_loads(ops, dtype, M, N, K, eps):
+    """A product whose input is an RMS norm that has not been evaluated: with few rows the streaming products norm the
+    rows themselves (no centring, w + 1 as the factor), with more rows the norm is evaluated first; both against the
+    oracle and against each other."""
+    from mini_llm_b200.engine.context import Workspace
+    ws = Workspace(torch.device(DEV), 64)
+    x = rnd(M + 3, K, seed=31, scale=2.0) + 0.7
+    w = rnd(K, seed=32, scale=0.2)
+    W = rnd(N, K, seed=33, scale=K ** -0.5, dtype=dtype)
+    rows = torch.tensor(list(range(M, 0, -1)), dtype=torch.int32, device=DEV)
+    gamma, beta = (w + 1.0).contiguous(), torch.zeros_like(w)
+    lazy = ops.NormedInput(x, gamma, beta, eps, rows, ws, dtype, rms=True)
+    out = torch.empty(M, N, device=DEV, dtype=dtype)
+    n0 = ops.launches
+    ops.linear(lazy, W, None, out=out)
+    fused = ops.launches - n0 == 1
+    assert fused == (M <= 16)
+    h = P.rms_norm(x.double().cpu()[rows.long().cpu()], w.double().cpu(), eps, True)
+    if dtype == torch.bfloat16:
+        h = P.to_bf16(h)
+    want = h @ W.double().cpu().t()
+    tol = 3e-5 if dtype == torch.float32 else 1.2e-2
+    assert (out.double().cpu() - want).abs().max() < tol * max(1.0, want.abs().max().item())
+    # the same through the norm kernel and the plain product
+    hn = torch.empty(M, K, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, w, eps, hn, rows=rows, unit_offset=True)
+    out2 = torch.empty(M, N, device=DEV, dtype=dtype)
+    ops.linear(hn, W, None, out=out2)
+    assert (out.double() - out2.double()).abs().max() < tol * max(1.0, want.abs().max().item())
+    ops.check_device_errors()
+
+
 def test_rmsnorm_keeps_eps_inside_the_root(ops):
     # a row of tiny values: x / sqrt(mean + eps) is far from x / (sqrt(mean) + eps)
     x = torch.full((1, 64), 1e-4, device=DEV)
