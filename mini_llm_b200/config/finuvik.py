@@ -2,7 +2,8 @@
 
 A Finuvik model is a list of layers; every entry names its mixer's sizes and
 constants, its feed-forward (or none) and, optionally, another layer whose
-tensors it uses (``weights_of``) while keeping a cache and a state of its own.
+tensors it uses (``weights_of``) while keeping a cache and a state of its own
+(such a layer runs the other layer's parts, with that layer's constants).
 Nothing is assumed equal between layers: every size is read per entry.
 """
 from __future__ import annotations
@@ -152,10 +153,12 @@ class FinuvikConfig(ModelConfig):
         for i, lay in enumerate(layers):
             j = cfg.weight_layer(i)
             if j != i:
-                a, b = copy.copy(lay), copy.copy(layers[j])
-                a.weights_of = b.weights_of = None
-                if a != b:
-                    raise ConfigError(f"config.json: layers[{i}] uses the tensors of layers[{j}] but differs from it")
+                # the layer runs layer j's parts, so layer j's constants hold; sizes that differ cannot be served
+                a, b = lay, layers[j]
+                sizes = lambda l: (l.left.heads, l.left.kv_heads, l.left.dim, l.left.vdim, l.right.heads, l.right.dim,
+                                   l.right.vdim, l.ff)
+                if sizes(a) != sizes(b):
+                    raise ConfigError(f"config.json: layers[{i}] uses the tensors of layers[{j}] but differs from it in its sizes")
         return cfg
 
     def to_dict(self) -> Dict[str, Any]:

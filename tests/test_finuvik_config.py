@@ -55,7 +55,7 @@ def test_config_reads_every_size_and_constant():
     (lambda d: d["layers"][0]["mlp"].update(kind="routed"), "kind"),
     (lambda d: d["layers"][1].update(weights_of=7), "weights_of"),
     (lambda d: d["layers"][1].update(weights_of=1), "weights_of"),
-    (lambda d: d["layers"][1]["mixer"].update(left_scale=0.1), "differs"),
+    (lambda d: d["layers"][1]["mixer"]["right"].update(vdim=48), "differs"),
     (lambda d: d["layers"][0]["mixer"]["left"]["q_temp"].update(every=0), "every"),
     (lambda d: d.update(layers=[]), "layers"),
 ])
