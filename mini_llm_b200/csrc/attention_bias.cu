@@ -583,20 +583,40 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
     const int kp8 = dk / 8, vp8 = dv / 8;
 
+    // Which pieces of a tile this thread copies: the same (key, piece) pairs for every tile, so the divisions are
+    // made once.  A thread copies up to MMAX / 16 pieces of keys and as many of values per tile.
+    constexpr int SU = MMAX / 16;
+    int k_kp[SU], v_kp[SU];                                      // key | piece << 8, or -1
+#pragma unroll
+    for (int u = 0; u < SU; ++u) {
+        const int i = tid + u * 128;
+        k_kp[u] = i < MK * kp8 ? (i / kp8) | ((i % kp8) << 8) : -1;
+        v_kp[u] = i < MK * vp8 ? (i / vp8) | ((i % vp8) << 8) : -1;
+    }
+    const int ps_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;    // pages of a power of two: shifts
+    auto row_of = [&](int kp) -> size_t {                        // first element of key position kp's row, in rows
+        const int pg = ps_shift >= 0 ? kp >> ps_shift : kp / page_size;
+        const int off = ps_shift >= 0 ? kp & (page_size - 1) : kp % page_size;
+        return ((size_t)bt[pg] * Hkv + hk) * page_size + off;
+    };
     auto stage = [&](int j, int buf) {                           // key tile j into buffer buf
         bf* kd = Ks + buf * MK * krow;
         bf* vd = Vs + buf * MK * vrow;
-        for (int i = tid; i < MK * kp8; i += 128) {
-            const int key = i / kp8, piece = i % kp8, kp = j * MK + key;
-            const bool ok = kp <= pos_max && kp >= first_key;
-            const bf* src = ok ? k_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dk + piece * 8 : k_pages;
-            cp_async16(kd + key * krow + piece * 8, src, ok);
+#pragma unroll
+        for (int u = 0; u < SU; ++u) {
+            if (k_kp[u] >= 0) {
+                const int key = k_kp[u] & 255, piece = k_kp[u] >> 8, kp = j * MK + key;
+                const bool ok = kp <= pos_max && kp >= first_key;
+                cp_async16(kd + key * krow + piece * 8, ok ? k_pages + row_of(kp) * dk + piece * 8 : k_pages, ok);
+            }
         }
-        for (int i = tid; i < MK * vp8; i += 128) {
-            const int key = i / vp8, piece = i % vp8, kp = j * MK + key;
-            const bool ok = kp <= pos_max && kp >= first_key;
-            const bf* src = ok ? v_pages + (((size_t)bt[kp / page_size] * Hkv + hk) * page_size + kp % page_size) * dv + piece * 8 : v_pages;
-            cp_async16(vd + key * vrow + piece * 8, src, ok);
+#pragma unroll
+        for (int u = 0; u < SU; ++u) {
+            if (v_kp[u] >= 0) {
+                const int key = v_kp[u] & 255, piece = v_kp[u] >> 8, kp = j * MK + key;
+                const bool ok = kp <= pos_max && kp >= first_key;
+                cp_async16(vd + key * vrow + piece * 8, ok ? v_pages + row_of(kp) * dv + piece * 8 : v_pages, ok);
+            }
         }
         if (brow) {
             const int dist0 = pos0 - (j * MK + MK - 1);

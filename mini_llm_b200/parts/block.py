@@ -26,20 +26,18 @@ def pre_norm(layer, x, ctx, cache):
 register_part("arrangement", "pre_norm", lambda: pre_norm)
 
 
-LAZY_ROWS = 16      # rows up to which the streaming products take a norm into their loads (ops.NORM_FUSE_M)
-
-
 def parallel(layer, x, ctx, cache):
     """x += mixer(norm_a(x)) + ff(norm_b(x)): both norms read the same x, so everything that reads x runs before
-    anything adds to it.  With few rows (decode steps) both norms ride in the loads of the branches' first products:
+    anything adds to it.  With few, narrow rows (decode steps; the norms say when it pays) both norms ride in the loads of the branches' first products:
     the feed-forward's first product is issued before the mixer, whose last product changes x.  With many rows two
     RMS norms that differ only in their weights share one kernel."""
     if layer.ff is None:
         layer.mixer.forward(_norm(layer.mixer_norm, layer.mixer, x, ctx), ctx, cache, x)
         return x
-    lazy = (x.shape[0] <= LAZY_ROWS and getattr(layer.mixer_norm, "supports_lazy", False)
-            and getattr(layer.ff_norm, "supports_lazy", False) and getattr(layer.mixer, "accepts_lazy_norm", False)
-            and getattr(layer.ff, "accepts_lazy_norm", False) and hasattr(layer.ff, "project"))
+    pays = getattr(layer.mixer_norm, "lazy_pays", None), getattr(layer.ff_norm, "lazy_pays", None)
+    lazy = (pays[0] is not None and pays[1] is not None and pays[0](x.shape[0]) and pays[1](x.shape[0])
+            and getattr(layer.mixer, "accepts_lazy_norm", False) and getattr(layer.ff, "accepts_lazy_norm", False)
+            and hasattr(layer.ff, "project"))
     if lazy:
         gu = layer.ff.project(layer.ff_norm.forward(x, ctx, lazy=True, name="norm_out_b"), ctx)
         layer.mixer.forward(layer.mixer_norm.forward(x, ctx, lazy=True), ctx, cache, x)
