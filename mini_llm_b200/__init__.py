@@ -1,4 +1,4 @@
-"""mini_llm_b200: a small, whole inference engine for one B200 (sm_100a): GPT-2 and Finuvik.
+"""mini_llm_b200: a small, whole inference engine for one B200 (sm_100a): GPT-2, Finuvik and Falisun.
 
 Configuration and registry (``config``), safetensors weights (``weights``), model
 parts and their assembly (``parts``, ``models``), paged cache manager (``cache``),
@@ -7,9 +7,10 @@ hand-written CUDA kernels (``csrc``, reached through ``ops``).
 """
 from .config.base import (ConfigError, EngineConfig, config_from_dict, load_config, register_architecture,
                           registered_architectures)
-from .parts import attention, block, embedding, head, mlp, norm, positions, projected, recurrent  # noqa: F401  (register the parts)
+from .parts import (attention, block, embedding, head, join, latent, mlp, moe, norm, positions, projected,  # noqa: F401
+                    recurrent, ssm)                                                                        # (register the parts)
 from .parts.base import register_part
-from .models import finuvik, gpt2  # noqa: F401  (register GPT2LMHeadModel and Finuvik)
+from .models import falisun, finuvik, gpt2  # noqa: F401  (register GPT2LMHeadModel, Finuvik and Falisun)
 from .weights.random_init import write_random_model
 from .sampling.params import SamplingParams
 from .engine.request import Request, RequestState, Response

@@ -31,6 +31,7 @@ class PagedNeed:
     head_dim: int
     window: Optional[int] = None      # None: every past token stays visible
     v_head_dim: Optional[int] = None  # size of a value row when it differs from a key row's (None: head_dim)
+    values_in_keys: bool = False      # a token's value is a part of its key row (a cache of latents): no value pool
 
     @property
     def value_dim(self) -> int:
@@ -65,7 +66,9 @@ class CacheGroup:
     def allocate(self, dtype, device) -> None:
         import torch
         n, nd, P = len(self.layers), self.need, self.allocator.num_pages
-        if nd.value_dim == nd.head_dim:
+        if nd.values_in_keys:
+            self.pool_k = torch.zeros((n, P, nd.kv_heads, self.page_size, nd.head_dim), dtype=dtype, device=device)
+        elif nd.value_dim == nd.head_dim:
             self.pool = torch.zeros((n, 2, P, nd.kv_heads, self.page_size, nd.head_dim), dtype=dtype, device=device)
         else:
             self.pool_k = torch.zeros((n, P, nd.kv_heads, self.page_size, nd.head_dim), dtype=dtype, device=device)
@@ -76,10 +79,13 @@ class CacheGroup:
         return self.pool[li, 0] if self.pool is not None else self.pool_k[li]
 
     def v_pages(self, li: int):
+        if self.need.values_in_keys:
+            return None
         return self.pool[li, 1] if self.pool is not None else self.pool_v[li]
 
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.layers) * self.need.kv_heads * (self.need.head_dim + self.need.value_dim) * element_size
+        per_head = self.need.head_dim + (0 if self.need.values_in_keys else self.need.value_dim)
+        return len(self.layers) * self.need.kv_heads * per_head * element_size
 
 
 @dataclass

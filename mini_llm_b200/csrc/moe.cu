@@ -1,0 +1,268 @@
+// A routed feed-forward (mixture of experts) without a host round trip:
+//
+//   moe_route       a warp per token: router logits in 32-bit, softmax over all experts, the best `keep` of `n_groups`
+//                   equal groups of neighbouring experts (a group's score is its largest), the `top` best experts inside
+//                   those groups (the lowest index wins among equals), weights = scores / (their sum + 1e-20).
+//   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets.
+//   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e, 32 pairs x 64 columns per CTA; a CTA finds its
+//                   expert from the offsets on the device, so the grid depends on the number of pairs only.  `gated`:
+//                   W_e is [2F, K] (gate rows, then up rows) and the result is silu(gate) * up.
+//   moe_combine     y[t] (+)= sum_k weight[t][k] * pair_out[t * top + k], in the order of k.
+// A row of a product depends on that row's input only, so a token's result does not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_E = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups, int keep,
+                 int* idx, float* wout) {
+    __shared__ float sc[4][MAX_E];
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= Tn) return;
+    float* s = sc[warp];
+    const T* x = h + (size_t)t * ld;
+    for (int e = 0; e < E; ++e) {
+        const T* w = Wr + (size_t)e * D;
+        float a = 0.f;
+        for (int d = lane; d < D; d += 32) a = fmaf(to_f32(x[d]), to_f32(w[d]), a);
+        a = warp_sum(a);
+        if (lane == 0) s[e] = a;
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float v = expf(s[e] - mx);
+        s[e] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    __syncwarp();
+    if (lane != 0) return;
+    // experts outside the kept groups are marked by a negative score (scores are >= 0)
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        unsigned long long kept_lo = 0ull;          // groups are few: a bit set over up to 64 of them, else a scan
+        for (int k = 0; k < keep; ++k) {
+            int best = -1;
+            float bv = -1.f;
+            for (int g = 0; g < n_groups; ++g) {
+                if (g < 64 && ((kept_lo >> g) & 1ull)) continue;
+                float gm = -1.f;
+                for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
+                if (gm > bv) { bv = gm; best = g; }
+            }
+            if (best >= 0) kept_lo |= 1ull << best;
+        }
+        for (int g = 0; g < n_groups; ++g)
+            if (!((kept_lo >> g) & 1ull))
+                for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -1.f - s[e];
+    }
+    float wsum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (s[e] > bv) { bv = s[e]; best = e; }
+        idx[(size_t)t * top + k] = best;
+        wout[(size_t)t * top + k] = bv;
+        wsum += bv;
+        s[best] = -8.f;                              // taken
+    }
+    for (int k = 0; k < top; ++k) wout[(size_t)t * top + k] = wout[(size_t)t * top + k] / (wsum + 1e-20f);
+}
+
+// one CTA of 1024 threads: offsets[E + 1], sorted[n] = pair ids ordered by expert (pairs of one expert in pair order)
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
+    __shared__ int cnt[MAX_E + 1];
+    pdl_wait();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = cnt[e];
+            cnt[e] = run;
+            run += c;
+        }
+        cnt[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = cnt[e];
+    // a warp per expert walks the pairs in order: a stable order without atomics
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nw) {
+        int at = cnt[e];
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool mine = i < n && idx[i] == e;
+            const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+            if (mine) sorted[at + __popc(ballot & ((1u << lane) - 1u))] = i;
+            at += __popc(ballot);
+        }
+    }
+}
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
+                   const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated) {
+    __shared__ float As[32][33];
+    __shared__ float Ws[64][33];
+    __shared__ float Us[64][33];
+    __shared__ int rows_a[32], rows_o[32];
+    __shared__ int s_e, s_r0, s_cnt;
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, e = 0, found = -1, r0 = 0, c = 0;
+        for (; e < E; ++e) {
+            const int lo = offsets[e], n = offsets[e + 1] - lo;
+            const int tiles = (n + 31) / 32;
+            if (tile < tiles) { found = e; r0 = lo + tile * 32; c = min(32, n - tile * 32); break; }
+            tile -= tiles;
+        }
+        s_e = found; s_r0 = r0; s_cnt = c;
+    }
+    __syncthreads();
+    const int e = s_e, cnt = s_cnt;
+    if (e < 0) return;
+    if (threadIdx.x < 32) {
+        const int i = s_r0 + threadIdx.x;
+        const int pair = threadIdx.x < cnt ? sorted[i] : 0;
+        rows_a[threadIdx.x] = a_div > 0 ? pair / a_div : i;
+        rows_o[threadIdx.x] = out_by_pair ? pair : i;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * 64;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const size_t wrows = gated ? (size_t)2 * N : (size_t)N;
+    const TW* We = W + (size_t)e * wrows * K;
+    float acc[2][4] = {}, acu[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        for (int i = threadIdx.x; i < 32 * 32; i += 256) {
+            const int r = i >> 5, c = i & 31;
+            As[r][c] = (r < cnt && k0 + c < K) ? to_f32(A[(size_t)rows_a[r] * lda + k0 + c]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < 64 * 32; i += 256) {
+            const int r = i >> 5, c = i & 31;
+            const bool ok = n0 + r < N && k0 + c < K;
+            Ws[r][c] = ok ? to_f32(We[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+            if (gated) Us[r][c] = ok ? to_f32(We[(size_t)(N + n0 + r) * K + k0 + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < 32; ++kk) {
+            const float a0 = As[ty * 2][kk], a1 = As[ty * 2 + 1][kk];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float w = Ws[tx + 16 * i][kk];
+                acc[0][i] = fmaf(a0, w, acc[0][i]);
+                acc[1][i] = fmaf(a1, w, acc[1][i]);
+            }
+            if (gated) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float u = Us[tx + 16 * i][kk];
+                    acu[0][i] = fmaf(a0, u, acu[0][i]);
+                    acu[1][i] = fmaf(a1, u, acu[1][i]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int r = ty * 2 + j;
+        if (r >= cnt) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = n0 + tx + 16 * i;
+            if (n >= N) continue;
+            float v = acc[j][i];
+            if (gated) v = v / (1.0f + expf(-v)) * acu[j][i];
+            out[(size_t)rows_o[r] * ldo + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* pair_out, const float* w, float* y, long long ldy, int Tn, int D, int top, int accumulate) {
+    pdl_wait();
+    const long long total = (long long)Tn * D;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / D), d = (int)(i % D);
+        float a = accumulate ? y[(size_t)t * ldy + d] : 0.f;
+        for (int k = 0; k < top; ++k) a = fmaf(w[(size_t)t * top + k], pair_out[((size_t)t * top + k) * D + d], a);
+        y[(size_t)t * ldy + d] = a;
+    }
+}
+
+}  // namespace
+
+MLLM_EXPORT int mllm_moe_max_experts() { return MAX_E; }
+
+MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int Tn, int D, int E, int top, int n_groups,
+                               int keep, int* idx, float* w, int* offsets, int* sorted, int dtype, cudaStream_t stream) {
+    if (Tn <= 0) return 0;
+    if (E < 1 || E > MAX_E || top < 1 || top > E) return mllm_fail(1, "moe_route: %d experts (at most %d), top %d", E, MAX_E, top);
+    if (n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || n_groups > 64)
+        return mllm_fail(1, "moe_route: %d experts in %d groups (at most 64), %d kept", E, n_groups, keep);
+    if (keep * (E / n_groups) < top) return mllm_fail(1, "moe_route: %d kept groups of %d experts cannot give %d", keep, E / n_groups, top);
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(moe_route_kernel<float>, dim3((Tn + 3) / 4), dim3(128), 0, stream, true, (const float*)h, ld,
+                              (const float*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(moe_route_kernel<__nv_bfloat16>, dim3((Tn + 3) / 4), dim3(128), 0, stream, true,
+                              (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
+    else
+        return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
+    MLLM_CUDA(mllm_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, true, (const int*)idx, Tn * top, E, offsets, sorted));
+    return 0;
+}
+
+// kind 0: A in `dtype`, gated, out in `dtype` (the experts' first product with its activation);
+// kind 1: A in `dtype`, out 32-bit (the experts' second product).
+MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, const int* offsets,
+                                 const int* sorted, int n_pairs, int E, int N, int K, int a_div, int out_by_pair, int kind,
+                                 int dtype, cudaStream_t stream) {
+    if (n_pairs <= 0 || N <= 0) return 0;
+    const dim3 grid((n_pairs + 31) / 32 + E, (N + 63) / 64), block(256);
+    if (grid.y > 65535) return mllm_fail(1, "moe_grouped: too many columns");
+    const int gated = kind == 0;
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(moe_grouped_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)A, lda,
+                              (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated));
+    else if (dtype == MLLM_BF16 && kind == 0)
+        MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, true,
+                              (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E,
+                              N, K, a_div, out_by_pair, gated));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, block, 0, stream, true,
+                              (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K,
+                              a_div, out_by_pair, gated));
+    else
+        return mllm_fail(1, "moe_grouped: unknown dtype code %d", dtype);
+    return 0;
+}
+
+MLLM_EXPORT int mllm_moe_combine(const float* pair_out, const float* w, float* y, long long ldy, int Tn, int D, int top,
+                                 int accumulate, cudaStream_t stream) {
+    if (Tn <= 0) return 0;
+    const long long total = (long long)Tn * D;
+    const int grid = (int)((total + 255) / 256 < 16384 ? (total + 255) / 256 : 16384);
+    MLLM_CUDA(mllm_launch(moe_combine_kernel, dim3(grid), dim3(256), 0, stream, true, pair_out, w, y, ldy, Tn, D, top,
+                          accumulate));
+    return 0;
+}

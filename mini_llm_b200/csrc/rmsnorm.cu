@@ -121,7 +121,36 @@ gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long lon
     }
 }
 
+// x[r] += (y[r] / sqrt(mean(y[r]^2) + eps) * w) * ls: a branch's result, normed, scaled per column and added to the
+// 32-bit residual stream in one pass (ls may be absent).
+__global__ void __launch_bounds__(256)
+norm_scale_add_kernel(const float* y, long long y_stride, const float* __restrict__ w, const float* __restrict__ ls, float* x,
+                      long long x_stride, int D, float eps) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
+    const float* yr = y + (size_t)blockIdx.x * y_stride;
+    float* xr = x + (size_t)blockIdx.x * x_stride;
+    float q = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) q = fmaf(yr[d], yr[d], q);
+    const float r = sqrtf(block_sum(q, scratch) / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = yr[d] / r * w[d];
+        if (ls) v *= ls[d];
+        xr[d] += v;
+    }
+}
+
 }  // namespace
+
+MLLM_EXPORT int mllm_norm_scale_add(const float* y, long long y_stride, const float* w, const float* ls, float* x,
+                                    long long x_stride, int R, int D, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (D <= 0) return mllm_fail(1, "norm_scale_add: width %d", D);
+    const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
+    MLLM_CUDA(mllm_launch(norm_scale_add_kernel, dim3(R), dim3(threads), 0, stream, true, y, y_stride, w, ls, x, x_stride, D, eps));
+    return 0;
+}
 
 MLLM_EXPORT int mllm_rmsnorm(const float* x, long long x_stride, const int* rows, const float* w1, const float* w2,
                              void* out1, void* out2, long long out_stride, int heads, int R, int D, float eps,

@@ -300,7 +300,8 @@ class ModelRunner:
             self._graph_seen.clear()
             self._graph_families.clear()
             self._graph_version = self._buffer_version()
-        key = (ctx.layout.key(), ops.decode_splits(ctx.max_ctx_len) if ctx.decode_only else 0)
+        key = (ctx.layout.key(), ops.decode_splits(ctx.max_ctx_len) if ctx.decode_only else 0,
+               ops.latent_splits(ctx.max_ctx_len))      # every host-side number a launch's grid depends on
         g = self._graphs.get(key)
         if g is not None:
             g[0].replay()

@@ -101,6 +101,24 @@ def _signatures(lib):
         "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_int, c_void_p],
+        "mllm_norm_scale_add": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_void_p],
+        "mllm_latent_prepare": [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        "mllm_headwise_linear": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_void_p],
+        "mllm_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_ssd_conv": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_ssd_scan": [c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_gated_group_norm": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
+                                  c_void_p],
+        "mllm_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_int, c_void_p],
+        "mllm_moe_grouped": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p],
+        "mllm_moe_combine": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -831,6 +849,240 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
     if impl == "split":
         global launches
         launches += 1           # the kernel that merges the splits
+
+
+
+# --------------------------------------------------------------------------- joining a branch's result to the residual
+def norm_scale_add(y, weight, scale, x, eps: float) -> None:
+    """x += (y / sqrt(mean(y^2) + eps) * weight) * scale, row by row, all 32-bit; ``scale`` (a vector) may be None."""
+    _cuda("y", y, torch.float32, contiguous=False)
+    _cuda("x", x, torch.float32, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    if scale is not None:
+        _cuda("scale", scale, torch.float32)
+    R, D = x.shape
+    if tuple(y.shape) != (R, D) or weight.numel() != D or (scale is not None and scale.numel() != D):
+        raise KernelError(f"norm_scale_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {weight.numel()}")
+    _call("mllm_norm_scale_add", y.data_ptr(), _rows("y", y), weight.data_ptr(),
+          scale.data_ptr() if scale is not None else None, x.data_ptr(), _rows("x", x), R, D, float(eps), _stream())
+
+
+# --------------------------------------------------------------------------- attention over a cache of latents
+LATENT_MAX_RANK, LATENT_MAX_KEY = 512, 1024      # what csrc/latent_attention.cu takes
+_latent_split_keys = None
+
+
+def latent_prepare(proj, q_off: int, dkv_off: Optional[int], ctx, slot_mapping, freq, mscale: float, norm_weight, eps: float,
+                   pages, qa, *, heads: int, dim: int, rot_dim: int, rank: int, rot_dims: int, write: bool) -> None:
+    """Per token of the step: the latent (columns dkv_off .. of ``proj``, RMS-normed with ``norm_weight``) and the shared
+    key part rotated at the token's position go to the token's cache row [rank | rot_dim | padding] (``dkv_off`` None or
+    ``write`` False: no row is written); every head's rotated query part goes, rotated, to columns rank.. of
+    qa [T, heads, rank + rot_dim] (32-bit).  Angles p * freq[i], cos and sin times ``mscale``, all 32-bit."""
+    _cuda("proj", proj, contiguous=False)
+    _cuda("qa", qa, torch.float32)
+    _cuda("freq", freq, torch.float32)
+    T = proj.shape[0]
+    row = 0
+    if dkv_off is not None and write:
+        _cuda("pages", pages, proj.dtype)
+        _cuda("norm_weight", norm_weight, torch.float32)
+        _cuda("slot_mapping", slot_mapping, torch.int32)
+        row = pages.shape[-1]
+        if pages.shape[1] != 1 or norm_weight.numel() != rank or slot_mapping.numel() != T:
+            raise KernelError("latent_prepare: the cache must have one key/value head and one slot per token")
+    else:
+        row = rank + rot_dim
+    if tuple(qa.shape) != (T, heads * (rank + rot_dim)) or freq.numel() * 2 != rot_dims:
+        raise KernelError(f"latent_prepare: qa {tuple(qa.shape)} for {heads} heads of {rank} + {rot_dim}")
+    wr = dkv_off is not None and write
+    _call("mllm_latent_prepare", proj.data_ptr(), _rows("proj", proj), int(q_off), int(dkv_off) if wr else -1, T, heads, dim,
+          rot_dim, rank, rot_dims, ctx.positions.data_ptr(), slot_mapping.data_ptr() if wr else None, freq.data_ptr(),
+          float(mscale), norm_weight.data_ptr() if wr else None, float(eps), pages.data_ptr() if wr else None, row,
+          qa.data_ptr(), int(wr), _dt(proj), _stream())
+
+
+def headwise_linear(x, x_head: int, weight, out, out_head: int, gate=None) -> None:
+    """out[t, h*out_head + n] = sum_k x[t, h*x_head + k] * weight[h, n, k], optionally times sigmoid(gate[t, h*N + n]):
+    a small product per head.  Either x has the weights' dtype and out is 32-bit, or x is 32-bit and out (and the
+    gate) have the weights' dtype."""
+    _cuda("x", x, contiguous=False)
+    _cuda("weight", weight)
+    _cuda("out", out, contiguous=False)
+    H, N, K = weight.shape
+    T = x.shape[0]
+    if out.shape[0] != T or x_head < K or out_head < N:
+        raise KernelError("headwise_linear: shapes do not fit the weights")
+    if x.dtype == weight.dtype and out.dtype == torch.float32 and gate is None:
+        mode = 0
+    elif x.dtype == torch.float32 and out.dtype == weight.dtype:
+        mode = 1
+        if gate is not None:
+            _cuda("gate", gate, weight.dtype, contiguous=False)
+    else:
+        raise KernelError(f"headwise_linear: x {x.dtype}, weight {weight.dtype}, out {out.dtype}")
+    _call("mllm_headwise_linear", x.data_ptr(), _rows("x", x), int(x_head), weight.data_ptr(), out.data_ptr(), _rows("out", out),
+          int(out_head), gate.data_ptr() if gate is not None else None, _rows("gate", gate) if gate is not None else 0,
+          T, H, N, K, mode, _dt(weight), _stream())
+
+
+def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int, scale: float) -> None:
+    """Causal softmax attention of qa [T, heads * dk] (32-bit) over cache rows pages [P, 1, page_size, row]: a token's row
+    holds its key (the first dk columns) and its value (the first ``rank`` columns) for all heads.
+    out[t, h] = sum_j softmax_j((qa[t, h] . row_j[:dk]) * scale) row_j[:rank], 32-bit [T, heads * rank]."""
+    global _latent_split_keys
+    _cuda("qa", qa, torch.float32)
+    _cuda("pages", pages)
+    _cuda("out", out, torch.float32)
+    _cuda("block_table", block_table, torch.int32, contiguous=False)
+    T = qa.shape[0]
+    dk = qa.shape[1] // heads
+    _, one, ps, row = pages.shape
+    if one != 1 or qa.shape[1] != heads * dk or tuple(out.shape) != (T, heads * rank) or not (rank <= dk <= row):
+        raise KernelError("latent_attention: shapes do not fit the cache rows")
+    if rank > LATENT_MAX_RANK or dk > LATENT_MAX_KEY:
+        raise KernelError(f"latent_attention: latent size {rank} (at most {LATENT_MAX_RANK}), key size {dk} (at most {LATENT_MAX_KEY})")
+    if _latent_split_keys is None:
+        _latent_split_keys = int(library().mllm_latent_split_keys())
+    need = max(1, -(-int(ctx.max_ctx_len) // _latent_split_keys))
+    nsplit = 1 << (need - 1).bit_length()       # a power of two: few distinct grids for captured graphs
+    part_o = ctx.ws.buf("latent_part_o", T * heads * nsplit, rank, torch.float32)
+    part_ml = ctx.ws.buf("latent_part_ml", T * heads * nsplit, 2, torch.float32)
+    _call("mllm_latent_attention", qa.data_ptr(), pages.data_ptr(), row, block_table.data_ptr(), _rows("block_table", block_table),
+          ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), nsplit, out.data_ptr(),
+          T, heads, rank, dk, ps, float(scale), _dt(pages), _stream())
+    global launches
+    launches += 1           # the kernel that merges the splits
+
+
+def latent_splits(max_ctx_len: int) -> int:
+    """Splits of the latent attention at a context length (part of a step's shape for captured graphs)."""
+    global _latent_split_keys
+    if _latent_split_keys is None:
+        _latent_split_keys = int(library().mllm_latent_split_keys())
+    need = max(1, -(-int(max_ctx_len) // _latent_split_keys))
+    return 1 << (need - 1).bit_length()
+
+
+# --------------------------------------------------------------------------- state-space mixer
+SSD_MAX_STATE_ROWS, SSD_MAX_TAPS = 256, 16       # what csrc/ssd.cu takes
+
+
+def ssd_conv(proj, off: int, weight, bias, state, conv_off: int, ctx, out, *, write_state: bool = True) -> None:
+    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * u[t - (taps-1) + j, c]) with u = proj[:, off : off + C] within a
+    request; inputs before the step's first token of a request come from state[slot, conv_off:] ([taps-1, C], oldest
+    first), which afterwards holds the request's last taps - 1 inputs.  out 32-bit [T, C]."""
+    _cuda("proj", proj, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    _cuda("bias", bias, torch.float32)
+    _cuda("state", state, torch.float32)
+    _cuda("out", out, torch.float32)
+    C, taps = weight.shape
+    T = proj.shape[0]
+    if tuple(out.shape) != (T, C) or bias.numel() != C or state.dim() != 2 or conv_off + (taps - 1) * C > state.shape[1]:
+        raise KernelError("ssd_conv: shapes do not fit")
+    _call("mllm_ssd_conv", proj.data_ptr(), _rows("proj", proj), int(off), weight.data_ptr(), bias.data_ptr(), state.data_ptr(),
+          state.stride(0), int(conv_off), ctx.token_seq.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(),
+          out.data_ptr(), T, ctx.S, C, taps, int(write_state), _dt(proj), _stream())
+    if write_state and taps > 1:
+        global launches
+        launches += 1
+
+
+def ssd_scan(xbc, proj, dt_off: int, dt_bias, A_log, D, state, ctx, y, *, heads: int, vdim: int, state_rows: int, groups: int,
+             write_state: bool = True) -> None:
+    """The selective state-space recurrence over the step's tokens, request by request and head by head:
+    dt = softplus(proj[:, dt_off + h] + dt_bias[h]); S <- exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x, with
+    x = xbc[:, h*vdim : (h+1)*vdim], B and C the group's rows after the x columns of xbc [T, heads*vdim + 2*groups*N]
+    (32-bit).  state [slots, >= heads*N*vdim] float32: S of head h at h*N*vdim, [N, vdim]; y [T, heads*vdim] 32-bit."""
+    _cuda("xbc", xbc, torch.float32)
+    _cuda("proj", proj, contiguous=False)
+    _cuda("state", state, torch.float32)
+    _cuda("y", y, torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("A_log", A_log), ("D", D)):
+        _cuda(name, t, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"ssd_scan: {name} has {t.numel()} entries for {heads} heads")
+    T = xbc.shape[0]
+    inner, N = heads * vdim, state_rows
+    if xbc.shape[1] != inner + 2 * groups * N or tuple(y.shape) != (T, inner) or state.dim() != 2 \
+            or state.shape[1] < heads * N * vdim or proj.shape[0] != T:
+        raise KernelError("ssd_scan: shapes do not fit")
+    if N > SSD_MAX_STATE_ROWS:
+        raise KernelError(f"ssd_scan: a state of {N} rows (at most {SSD_MAX_STATE_ROWS})")
+    _call("mllm_ssd_scan", xbc.data_ptr(), xbc.shape[1], inner, inner + groups * N, proj.data_ptr(), _rows("proj", proj),
+          int(dt_off), dt_bias.data_ptr(), A_log.data_ptr(), D.data_ptr(), state.data_ptr(), state.stride(0),
+          ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), y.data_ptr(), ctx.S, heads, N, vdim, groups, int(write_state),
+          _dt(proj), _stream())
+
+
+def gated_group_norm(y, z, weight, out, groups: int, eps: float) -> None:
+    """out = rms_norm(y * silu(z)) * weight with the norm taken over each of ``groups`` equal parts of a row on its own;
+    y 32-bit [T, W], z and out in the activation dtype (column slices are fine)."""
+    _cuda("y", y, torch.float32)
+    _cuda("z", z, contiguous=False)
+    _cuda("out", out, z.dtype, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    T, W = y.shape
+    if tuple(z.shape) != (T, W) or tuple(out.shape) != (T, W) or weight.numel() != W or W % groups:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    _call("mllm_gated_group_norm", y.data_ptr(), z.data_ptr(), _rows("z", z), weight.data_ptr(), out.data_ptr(),
+          _rows("out", out), T, W, int(groups), float(eps), _dt(z), _stream())
+
+
+# --------------------------------------------------------------------------- routed feed-forward
+MOE_MAX_EXPERTS = 512
+
+
+def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int = 1, keep: int = 1) -> None:
+    """Per row of h: softmax of the router's logits (32-bit) over all experts; the best ``keep`` of ``groups`` equal
+    groups of neighbours (by their largest score); the ``top`` best experts within them -> idx [T, top] (int32) and
+    weights [T, top] (scores over their sum + 1e-20).  Then the (row, choice) pairs ordered by expert:
+    offsets [E + 1], order [T * top]."""
+    _cuda("h", h, contiguous=False)
+    _cuda("router", router, h.dtype)
+    for name, t, dt in (("idx", idx, torch.int32), ("weights", weights, torch.float32), ("offsets", offsets, torch.int32),
+                        ("order", order, torch.int32)):
+        _cuda(name, t, dt)
+    T, D = h.shape
+    E = router.shape[0]
+    if router.shape[1] != D or idx.numel() != T * top or weights.numel() != T * top or offsets.numel() != E + 1 \
+            or order.numel() != T * top:
+        raise KernelError("moe_route: shapes do not fit")
+    _call("mllm_moe_route", h.data_ptr(), _rows("h", h), router.data_ptr(), T, D, E, int(top), int(groups), int(keep),
+          idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), _dt(h), _stream())
+    global launches
+    launches += 1           # the sort
+
+
+def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool) -> None:
+    """The experts' products over the pairs in ``order``.  ``first``: a [T, K] (row = pair // top), weight [E, 2F, K]
+    (gate rows, then up rows) -> out[i] = silu(gate) * up for the i-th pair in order, [T*top, F].  Otherwise: a [T*top, K]
+    in that order, weight [E, N, K] -> out[pair] [T*top, N] 32-bit, by pair id."""
+    _cuda("a", a, contiguous=False)
+    _cuda("weight", weight, a.dtype)
+    _cuda("out", out, contiguous=False)
+    E, rows, K = weight.shape
+    n_pairs = order.numel()
+    N = rows // 2 if first else rows
+    if a.shape[1] != K or tuple(out.shape) != (n_pairs, N) or offsets.numel() != E + 1:
+        raise KernelError("moe_grouped: shapes do not fit")
+    if (first and out.dtype != a.dtype) or (not first and out.dtype != torch.float32):
+        raise KernelError("moe_grouped: the first product keeps the dtype, the second gives 32-bit")
+    _call("mllm_moe_grouped", a.data_ptr(), _rows("a", a), weight.data_ptr(), out.data_ptr(), _rows("out", out),
+          offsets.data_ptr(), order.data_ptr(), n_pairs, E, N, K, int(top) if first else 0, 0 if first else 1,
+          0 if first else 1, _dt(a), _stream())
+
+
+def moe_combine(pair_out, weights, y, *, top: int, accumulate: bool) -> None:
+    """y[t] (+)= sum_k weights[t, k] * pair_out[t * top + k] (32-bit), in the order of k."""
+    _cuda("pair_out", pair_out, torch.float32)
+    _cuda("weights", weights, torch.float32)
+    _cuda("y", y, torch.float32, contiguous=False)
+    T, D = y.shape
+    if tuple(pair_out.shape) != (T * top, D) or weights.numel() != T * top:
+        raise KernelError("moe_combine: shapes do not fit")
+    _call("mllm_moe_combine", pair_out.data_ptr(), weights.data_ptr(), y.data_ptr(), _rows("y", y), T, D, int(top),
+          int(accumulate), _stream())
 
 
 REC_WIDE_MAX_ROWS = 128        # rows of a head's state that the kernel for prompt portions takes

@@ -21,6 +21,9 @@ Interfaces (all tensors are CUDA tensors on the engine's stream):
                  (rotations), a no-op for absolute tables; ``max_positions``.
 * Embedding:     ``forward(ctx, positions_part) -> x_f32[T,D]``.
 * Head:          ``forward(y[R,D], ctx) -> logits_f32[R,V]``.
+* Join:          ``forward(y_f32[T,D], x_f32[T,D], ctx)``: brings a branch's result y into the residual x
+                 (a norm and a scale on y, say).  Mixers and feed-forwards with ``can_overwrite = True``
+                 take ``accumulate=False`` and then write their result instead of adding it.
 """
 from __future__ import annotations
 
@@ -83,6 +86,13 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Join(Part):
+    category = "join"
+
+    def forward(self, y, x, ctx):  # pragma: no cover
+        raise NotImplementedError
+
+
 class Positions(Part):
     category = "positions"
     max_positions: Optional[int] = None
@@ -111,7 +121,7 @@ class Head(Part):
 
 _REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
     "norm": {}, "mixer": {}, "feed_forward": {}, "positions": {}, "embedding": {}, "head": {},
-    "arrangement": {},
+    "arrangement": {}, "join": {},
 }
 
 

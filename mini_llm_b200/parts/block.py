@@ -3,6 +3,8 @@
 "pre_norm" is the reference's block (src/model/gpt2_model.cu:271-365):
 x += mixer(norm(x)); x += ff(norm(x)), with the residual stream x in 32-bit.
 "parallel": x += mixer(norm_a(x)) + ff(norm_b(x)), both branches reading the same x.
+"sandwich": x = join_a(x, mixer(norm_a(x))); x = join_b(x, ff(norm_b(x))): a branch's result goes through the layer's
+join (a second norm and a scale per column, say) before it reaches x.
 """
 from __future__ import annotations
 
@@ -57,3 +59,30 @@ def parallel(layer, x, ctx, cache):
 
 
 register_part("arrangement", "parallel", lambda: parallel)
+
+
+def _branch(part, y, *args):
+    """Run a mixer or feed-forward so that y holds its result (not a sum with what y held)."""
+    if getattr(part, "can_overwrite", False):
+        part.forward(*args, y, accumulate=False)
+    else:
+        y.zero_()
+        part.forward(*args, y)
+
+
+def sandwich(layer, x, ctx, cache):
+    """x <- join(x, branch(norm(x))) for the mixer and then for the feed-forward: the branch writes a 32-bit buffer of
+    its own, and the layer's join (``LayerSpec.mixer_join`` / ``ff_join``) brings it into the residual stream."""
+    import torch
+    if layer.mixer_join is None or (layer.ff is not None and layer.ff_join is None):
+        raise RuntimeError("sandwich arrangement: the layer has no join for a branch")
+    y = ctx.ws.buf("branch_out", x.shape[0], x.shape[1], torch.float32)
+    _branch(layer.mixer, y, _norm(layer.mixer_norm, layer.mixer, x, ctx), ctx, cache)
+    layer.mixer_join.forward(y, x, ctx)
+    if layer.ff is not None:
+        _branch(layer.ff, y, _norm(layer.ff_norm, layer.ff, x, ctx), ctx)
+        layer.ff_join.forward(y, x, ctx)
+    return x
+
+
+register_part("arrangement", "sandwich", lambda: sandwich)

@@ -1,0 +1,96 @@
+"""A routed feed-forward: a mixture of small gated experts, of which each token uses a few.
+
+Router logits z = W_r h (32-bit), scores s = softmax(z) over all experts.  Experts form ``groups`` equal groups of
+neighbours; a group's score is its largest score and only experts of the best ``keep`` groups can be chosen
+(``groups`` = 1: no restriction).  The ``top`` experts with the largest scores are chosen, their weights are their
+scores divided by their sum (+ 1e-20), and the output is the weighted sum of the chosen experts' outputs, each
+W_down (act(W_gate h) * (W_up h)) without biases; a shared expert of the same form (``shared_size``, or None) runs
+for every token and is added.
+
+Nothing is read back by the host: a kernel routes and orders the (token, choice) pairs by expert, and the experts'
+products run over that order with a grid that depends on the number of pairs only, so the step can be captured in a
+CUDA graph.  The experts' matrices are stacked at bind: [E, 2F, D] (gate rows, then up rows) and [E, D, F].
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from .base import FeedForward, ParamSpec, register_part
+
+
+class MoEFeedForward(FeedForward):
+    can_overwrite = True
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, groups: int = 1, keep: int = 1,
+                 shared_size: Optional[int] = None, activation: str = "silu"):
+        self.hidden_size, self.num_experts, self.top = int(hidden_size), int(num_experts), int(top)
+        self.expert_size, self.groups, self.keep = int(expert_size), int(groups), int(keep)
+        self.shared_size = None if shared_size is None else int(shared_size)
+        if activation != "silu":
+            raise ValueError("MoEFeedForward: the experts' activation is silu")
+        self.activation = activation
+        if self.num_experts % self.groups or not (1 <= self.keep <= self.groups):
+            raise ValueError(f"MoEFeedForward: {self.num_experts} experts in {self.groups} groups, {self.keep} kept")
+        if not (1 <= self.top <= self.keep * (self.num_experts // self.groups)):
+            raise ValueError(f"MoEFeedForward: top {self.top} of {self.keep} groups of {self.num_experts // self.groups}")
+
+    def param_specs(self):
+        D, F = self.hidden_size, self.expert_size
+        p = {"router": ParamSpec((self.num_experts, D), "matrix")}
+        for e in range(self.num_experts):
+            p[f"expert{e}.gate"] = ParamSpec((F, D), "matrix")
+            p[f"expert{e}.up"] = ParamSpec((F, D), "matrix")
+            p[f"expert{e}.down"] = ParamSpec((D, F), "matrix")
+        if self.shared_size is not None:
+            p["shared.gate"] = ParamSpec((self.shared_size, D), "matrix")
+            p["shared.up"] = ParamSpec((self.shared_size, D), "matrix")
+            p["shared.down"] = ParamSpec((D, self.shared_size), "matrix")
+        return p
+
+    def kernel_limits(self, dtype: str):
+        from .. import ops
+        if self.num_experts > ops.MOE_MAX_EXPERTS or self.groups > 64:
+            return [f"routed feed-forward: {self.num_experts} experts in {self.groups} groups; the router kernel takes "
+                    f"{ops.MOE_MAX_EXPERTS} experts in up to 64 groups"]
+        return []
+
+    def bind(self, params, rt) -> None:
+        import torch
+        self.rt = rt
+        if not params:
+            return
+        E = self.num_experts
+        self.router = params["router"]
+        self.w_first = torch.stack([torch.cat([params[f"expert{e}.gate"], params[f"expert{e}.up"]], 0) for e in range(E)]).contiguous()
+        self.w_second = torch.stack([params[f"expert{e}.down"] for e in range(E)]).contiguous()
+        if self.shared_size is not None:
+            self.shared_first = torch.cat([params["shared.gate"], params["shared.up"]], 0).contiguous()
+            self.shared_down = params["shared.down"]
+
+    def forward(self, h, ctx, out_accum, accumulate: bool = True):
+        import torch
+        ops = self.rt.ops
+        if isinstance(h, ops.NormedInput):
+            h = h.materialize()
+        T, top, E = h.shape[0], self.top, self.num_experts
+        act = self.rt.act_dtype
+        idx = ctx.ws.buf("moe_idx", T, top, torch.int32)
+        wts = ctx.ws.buf("moe_weights", T, top, torch.float32)
+        order = ctx.ws.buf("moe_order", T, top, torch.int32)
+        offsets = ctx.ws.buf("moe_offsets", 1, E + 1, torch.int32)
+        ops.moe_route(h, self.router, idx, wts, offsets, order, top=top, groups=self.groups, keep=self.keep)
+        mid = ctx.ws.buf("moe_mid", T * top, self.expert_size, act)
+        ops.moe_grouped(h, self.w_first, mid, offsets, order, top=top, first=True)
+        pair_out = ctx.ws.buf("moe_pair_out", T * top, self.hidden_size, torch.float32)
+        ops.moe_grouped(mid, self.w_second, pair_out, offsets, order, top=top, first=False)
+        if self.shared_size is not None:
+            gu = ctx.ws.buf("ff_gate_up", T, 2 * self.shared_size, act)
+            ops.linear(h, self.shared_first, None, out=gu)
+            smid = ctx.ws.buf("ff_mid", T, self.shared_size, act)
+            ops.gated_act(gu, smid, self.activation)
+            ops.linear(smid, self.shared_down, None, out=out_accum, accumulate=accumulate)
+            accumulate = True
+        ops.moe_combine(pair_out, wts, out_accum, top=top, accumulate=accumulate)
+
+
+register_part("feed_forward", "moe", MoEFeedForward)

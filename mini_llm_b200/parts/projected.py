@@ -25,6 +25,7 @@ from .base import Mixer, get_part_factory, register_part
 
 class ProjectedMixer(Mixer):
     accepts_lazy_norm = True            # the first thing done with the input is a product
+    can_overwrite = True                # forward(..., accumulate=False) writes the result instead of adding it
     in_names: Sequence[str] = ()        # parameters stacked (by rows) into the input projection, in this order
     out_name: str = "out_weight"        # the output projection [hidden, core_width]
 
@@ -46,14 +47,15 @@ class ProjectedMixer(Mixer):
         if all(n in params for n in self.in_names) and self.in_names:
             self.in_weight = torch.cat([params[n] for n in self.in_names], 0).contiguous()
 
-    def forward(self, h, ctx, cache, out_accum):
+    def forward(self, h, ctx, cache, out_accum, accumulate: bool = True):
         ops = self.rt.ops
         T = h.shape[0]
-        proj = ctx.ws.buf("mix_proj", T, self.in_width, self.rt.act_dtype)
+        n_in = self.in_weight.shape[0]
+        proj = ctx.ws.buf("mix_proj", T, -(-n_in // 8) * 8, self.rt.act_dtype)[:, :n_in]    # rows stay 16-byte aligned
         ops.linear(h, self.in_weight, None, out=proj)
         mid = ctx.ws.buf("mix_core", T, self.core_width, self.rt.act_dtype)
         self.core(proj, ctx, cache, mid)
-        ops.linear(mid, getattr(self, self.out_name), None, out=out_accum, accumulate=True)
+        ops.linear(mid, getattr(self, self.out_name), None, out=out_accum, accumulate=accumulate)
 
 
 class ParallelMixer(Mixer):

@@ -51,7 +51,9 @@ class LayerSpec:
 
     ``arrangement`` names how they are wired (registry ``ARRANGEMENTS``), e.g.
     "pre_norm": x += mixer(norm(x)); x += ff(norm(x)); "parallel": both read the
-    same x.  ``ff`` and ``ff_norm`` are None for a layer without a feed-forward.
+    same x.  ``ff`` and ``ff_norm`` are None for a layer without a feed-forward.  ``mixer_join`` / ``ff_join`` (registry
+    category "join") say how a branch's result reaches the residual when that is more than a sum: a norm and a learned
+    scale per column on the result, say ("sandwich" arrangement); None: the branch adds itself.
     """
 
     mixer: PartSpec
@@ -59,6 +61,8 @@ class LayerSpec:
     mixer_norm: PartSpec
     ff_norm: Optional[PartSpec]
     arrangement: str = "pre_norm"
+    mixer_join: Optional[PartSpec] = None
+    ff_join: Optional[PartSpec] = None
 
 
 @dataclass
@@ -119,8 +123,12 @@ class ModelSpec:
         for i, l in enumerate(self.layers):
             yield f"layers.{i}.mixer_norm", l.mixer_norm
             yield f"layers.{i}.mixer", l.mixer
+            if l.mixer_join is not None:
+                yield f"layers.{i}.mixer_join", l.mixer_join
             if l.ff is not None:
                 yield f"layers.{i}.ff_norm", l.ff_norm
                 yield f"layers.{i}.ff", l.ff
+                if l.ff_join is not None:
+                    yield f"layers.{i}.ff_join", l.ff_join
         yield "final_norm", self.final_norm
         yield "head", self.head
