@@ -58,9 +58,10 @@ def rotary_frequencies(dims: int, base: float, scaling: Optional[dict]):
 
 
 def rotate(x, positions, dims: int, base: float, scaling: Optional[dict]):
-    """x [..., T, d]: the first ``dims`` entries are rotated in pairs (i, i + dims/2), the rest pass."""
+    """x [..., T, d]: the first ``dims`` entries are rotated in pairs (i, i + dims/2), the rest pass.  The design takes
+    the angle in 32-bit: the frequency rounded to float32, times the position, rounded to float32."""
     f, m = rotary_frequencies(dims, base, scaling)
-    a = positions.to(F64)[:, None] * f[None, :]
+    a = (positions.to(torch.float32)[:, None] * f.to(torch.float32)[None, :]).to(F64)
     cos, sin = torch.cos(a) * m, torch.sin(a) * m
     half = dims // 2
     u, v = x[..., :half], x[..., half:dims]
@@ -89,8 +90,10 @@ def latent_attention(h, w: Dict[str, torch.Tensor], m: dict, eps: float, kv=None
     qn = q[..., :dn]
     qr = rotate(q[..., dn:].transpose(0, 1), torch.arange(T), rot["dims"], rot["base"], rot.get("scaling")).transpose(0, 1)
     c, kr = kv if kv is not None else latent_kv(h, w, m, eps, store)
-    kn = store(c @ w["uk"].t()).view(T, H, dn)
-    v = store(c @ w["uv"].t()).view(T, H, dv)
+    # the engine never forms the heads' keys and values of cached tokens (it takes W_uk to the query and W_uv to the
+    # weighted sum of latents), so nothing is rounded here
+    kn = (c @ w["uk"].t()).view(T, H, dn)
+    v = (c @ w["uv"].t()).view(T, H, dv)
     s = (torch.einsum("ihd,jhd->hij", qn, kn) + torch.einsum("ihd,jd->hij", qr, kr)) * m["scale"]
     mask = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
     s = s.masked_fill(~mask[None], float("-inf"))
@@ -150,8 +153,11 @@ def mamba2(h, w: Dict[str, torch.Tensor], m: dict, eps: float, store: Callable =
 
 
 # ------------------------------------------------------------------------------------------- feed-forward
-def gated_expert(h, w: Dict[str, torch.Tensor], prefix: str, store: Callable = _keep):
-    return store(silu(store(h @ w[prefix + "gate"].t())) * store(h @ w[prefix + "up"].t())) @ w[prefix + "down"].t()
+def gated_expert(h, w: Dict[str, torch.Tensor], prefix: str, store: Callable = _keep, halves_stored: bool = False):
+    """W_down (silu(W_gate h) * (W_up h)).  ``halves_stored``: the engine hands the two halves from a product to an
+    activation kernel (the shared expert); the routed experts' product applies the activation itself."""
+    inner = store if halves_stored else _keep
+    return store(silu(inner(h @ w[prefix + "gate"].t())) * inner(h @ w[prefix + "up"].t())) @ w[prefix + "down"].t()
 
 
 def route(h, router, r: dict):
@@ -181,7 +187,7 @@ def mixture_of_experts(h, w: Dict[str, torch.Tensor], mlp: dict, store: Callable
             if rows.numel():
                 out[rows] += weights[rows, k][:, None] * gated_expert(h[rows], w, f"e{e}.", store)
     if mlp.get("shared"):
-        out = out + gated_expert(h, w, "shared.", store)
+        out = out + gated_expert(h, w, "shared.", store, halves_stored=True)
     return out
 
 
