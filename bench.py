@@ -40,8 +40,8 @@ with "impl": "reference" and "dtype": "fp32".  The reference holds at most 16 re
 (more are cut) and there is no batch-64 point.  Where it cannot be built or run the line is
 {"impl": "reference", "unavailable": "<why>"}.
 
-``--compare-designs [small,medium,large]`` measures the engine's other design, Finuvik, beside GPT-2 at equal
-width, depth, head count and head size (bfloat16 unless --dtype is given).
+``--compare-designs [small,medium,large]`` measures the engine's other designs, Finuvik and Falisun, beside GPT-2 at
+equal width, depth and head count (bfloat16 unless --dtype is given; ``--designs gpt2,falisun`` picks some of them).
 
 ``--profile-step prefill|decode [--kernel-times]`` runs one small eager step (for a profiler, or to
 print each kernel's share of the step from CUDA events); ``--workload medium|xl`` runs the
@@ -316,13 +316,13 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: b
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = dict(SMALL, n_layer=layers)
-    if design == "finuvik":                      # the same step of Finuvik at the "small" comparison size
-        cfg = design_configs("small")["finuvik"]
+    if design in ("finuvik", "falisun"):         # the same step of the other designs at the "small" comparison size
+        cfg = design_configs("small")[design]
         cfg["layers"] = cfg["layers"][:layers]
-        cfg["n_positions"], cfg["vocab_size"] = cfg["max_positions"], cfg["vocab"]      # the names used below
+        cfg["n_positions"], cfg["vocab_size"] = DESIGN_POSITIONS, cfg["vocab"]      # the names used below
     times = None
     with tempfile.TemporaryDirectory(prefix="mini_llm_prof_") as d:
-        m.write_random_model({k: v for k, v in cfg.items() if design != "finuvik" or k not in ("n_positions", "vocab_size")},
+        m.write_random_model({k: v for k, v in cfg.items() if design == "gpt2" or k not in ("n_positions", "vocab_size")},
                              0, d, dtype=dtype)
         n = cfg["n_positions"]
         B = 2 if kind == "prefill" else batch
@@ -446,7 +446,30 @@ def design_configs(size: str):
                  mlp=dict(ff=z["gated_inner"], kind="dense"))
     finuvik = dict(architecture="Finuvik", width=D, vocab=DESIGN_VOCAB, max_positions=DESIGN_POSITIONS,
                    norm=dict(eps=1e-5), layers=[dict(layer) for _ in range(L)])
-    return {"gpt2": gpt2, "finuvik": finuvik}
+    # Falisun at the same width, depth and head count: Mamba-2 layers (inner width 2 D in heads of 64, 128 state rows)
+    # alternate with latent-attention layers (a latent of D/2 up to 512 with dh/2 rotated columns; from the second one on
+    # they read the first one's cache rows); the routed feed-forward has 8 experts of a quarter of Finuvik's inner
+    # size, two per token, and a shared expert of half of it, so a token passes as many feed-forward weights
+    rank = min(512, D // 2)
+    yarn = dict(factor=8.0, original=512, fast=32.0, slow=1.0)
+    F = z["gated_inner"]
+    ffn = dict(kind="moe", router=dict(experts=8, top=2, groups=dict(count=4, keep=2)), expert=dict(ff=F // 4 // 8 * 8),
+               shared=dict(ff=F // 2 // 8 * 8))
+    fl, first = [], None
+    for i in range(L):
+        if i % 2 == 0:
+            mixer = dict(heads=2 * D // 64, vdim=64, state=128, groups=1, conv=4, norm_groups=1)
+            fl.append(dict(type="mamba2", mixer=mixer, mlp=ffn))
+        else:
+            mixer = dict(heads=H, dim=dh, rot_dim=dh // 2, vdim=dh, kv_rank=rank, scale=(dh + dh // 2) ** -0.5,
+                         rot=dict(base=10000.0, dims=dh // 2, scaling=yarn))
+            if first is None:
+                first = i
+            else:
+                mixer["kv_from"] = first
+            fl.append(dict(type="latent_attention", mixer=mixer, mlp=ffn))
+    falisun = dict(architecture="Falisun", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), layers=fl)
+    return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun}
 
 
 def _design_model(model_dir, dtype, batch, tokens):
@@ -550,9 +573,9 @@ def design_decode(model_dir, dtype, batch, steps):
                 kernels=kernels)
 
 
-def run_compare_designs(sizes, dtype: str, batch: int, steps: int) -> int:
-    """Prefill and decode throughput of Finuvik beside GPT-2 (the closest model of the engine) at equal width, depth,
-    head count and head size, random weights; one JSON line per size.  Per kernel entry point the line carries the
+def run_compare_designs(sizes, dtype: str, batch: int, steps: int, designs=None) -> int:
+    """Prefill and decode throughput of Finuvik and Falisun beside GPT-2 at equal width, depth and head count, random
+    weights; one JSON line per size.  Per kernel entry point the line carries the
     microseconds of one eager step, from which the rooflines of the like kernels are compared."""
     import torch
     import mini_llm_b200 as m
@@ -562,6 +585,8 @@ def run_compare_designs(sizes, dtype: str, batch: int, steps: int) -> int:
         line = {"compare_designs": size, "dtype": dtype, "batch": batch, "decode_steps": steps,
                 "sizes": DESIGN_SIZES[size], "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]}}
         for name, cfg in design_configs(size).items():
+            if designs and name not in designs:
+                continue
             with tempfile.TemporaryDirectory(prefix="mini_llm_cmp_") as d:
                 m.write_random_model(cfg, 0, d, dtype=dtype)
                 pf = design_prefill(d, dtype)
@@ -707,8 +732,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64, prefill and other-precision measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
-    ap.add_argument("--design", choices=["gpt2", "finuvik"], default="gpt2",
-                    help="with --profile-step: the model whose step is run (finuvik: the 'small' size of --compare-designs)")
+    ap.add_argument("--design", choices=["gpt2", "finuvik", "falisun"], default="gpt2",
+                    help="with --profile-step: the model whose step is run (finuvik, falisun: the 'small' size of --compare-designs)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --profile-step: time every launch of one eager step with CUDA events and print the shares")
     ap.add_argument("--attention", choices=["auto", "mma_sync"], default="auto",
@@ -716,8 +741,9 @@ def main() -> int:
     ap.add_argument("--workload", choices=["medium", "xl"],
                     help="run a continuous-batching workload of GPT-2 medium or XL instead of the benchmark")
     ap.add_argument("--compare-designs", nargs="?", const="small,medium,large", metavar="SIZES",
-                    help="measure Finuvik beside GPT-2 at equal sizes (a comma list of small, medium, large) instead of "
-                         "the benchmark: prefill of 2 x 1024 tokens and decode at --batch, one JSON line per size")
+                    help="measure Finuvik and Falisun beside GPT-2 at equal sizes (a comma list of small, medium, large) "
+                         "instead of the benchmark: prefill of 2 x 1024 tokens and decode at --batch, one JSON line per size")
+    ap.add_argument("--designs", default="", help="with --compare-designs: a comma list of gpt2, finuvik, falisun (default: all)")
     args = ap.parse_args()
     if args.compare_designs:
         sizes = [z for z in args.compare_designs.split(",") if z]
@@ -726,7 +752,7 @@ def main() -> int:
             print(f"bench.py: unknown size(s) {bad}; known: {sorted(DESIGN_SIZES)}")
             return 2
         return run_compare_designs(sizes, "bfloat16" if args.dtype == "float32" and "--dtype" not in sys.argv else args.dtype,
-                                   args.batch, min(args.steps, 128))
+                                   args.batch, min(args.steps, 128), [z for z in args.designs.split(",") if z])
     if args.attention == "mma_sync":
         from mini_llm_b200 import ops
         ops.use_tcgen05_attention = False

