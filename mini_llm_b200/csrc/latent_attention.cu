@@ -9,17 +9,17 @@
 //                    and columns R.. of qa.
 //   headwise_linear  out[t][h][n] = sum_k in[t][h][k] W[h][n][k] (optionally times sigmoid(gate[t][h][n])):
 //                    the absorbed query (W = W_uk^T per head) and the head outputs (W = W_uv per head, with the gate).
-//   latent_attention one CTA per (split of 256 keys, token, block of 8 heads): key rows are staged once for all the
+//   latent_attention one CTA per (split of `span` keys, token, block of 8 heads): key rows are staged once for all the
 //                    heads of the block in chunks of 32 that start at multiples of 32 from position 0; a warp is a
-//                    head, its lanes are the 32 keys for the scores and 32 latent columns at a time for the weighted
+//                    head, its lanes are the 32 keys for the scores and 64 latent columns at a time for the weighted
 //                    sum; online softmax in 32-bit with expf.  Partial (o, m, l) per split, merged in split order by
-//                    latent_merge.  Splits and chunks are fixed ranges of positions, so a token's sums run in the same
-//                    order whether it came in a prompt portion, alone, or in a batch.
+//                    latent_merge.  Splits and chunks are fixed ranges of positions, so at one span a token's sums run
+//                    in the same order whether it came in a prompt portion, alone, or in a batch (the caller takes
+//                    short splits for steps of single tokens, to fill the GPU, and long ones otherwise).
 #include "common.cuh"
 
 namespace {
 
-constexpr int SPLIT = 256;      // keys per split
 constexpr int HB = 8;           // heads (warps) per CTA
 constexpr int MAX_R = 512;      // largest latent size
 constexpr int MAX_DK = 1024;    // largest R + dr
@@ -130,63 +130,88 @@ headwise_linear_kernel(const TI* in, long long ld_in, int in_head, const TW* __r
     }
 }
 
-// grid (splits, tokens, head blocks); dynamic shared memory: HB * dk floats of queries, then 32 key rows of `kw` words.
+// grid (splits, tokens, head blocks); dynamic shared memory: HB * dkp floats of queries, then two chunks of 32 key rows
+// of `kw` 32-bit words each (kw = a row's words + 4: rows stay 16-byte aligned for cp.async and 128-bit reads, and eight
+// lanes reading 16 bytes of eight consecutive rows touch all 32 banks).  A CTA walks the keys [split * span, ...) of its
+// token in chunks of 32, the next chunk's rows in flight (cp.async) while the current one is used.
+__device__ __forceinline__ void cp16(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
 template <typename T, int NACC>
 __global__ void __launch_bounds__(HB * 32)
 latent_attention_kernel(const float* qa, const T* pages, int row, const int* block_table, int bt_stride,
                         const int* token_seq, const int* positions, float* part_o, float* part_ml, int nsplit, int H,
-                        int R, int dk, int ps, float scale, int kw) {
+                        int R, int dk, int ps, float scale, int kw, int span) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int EPW = 4 / sizeof(T);                  // elements per 32-bit word
+    constexpr int V = 16 / sizeof(T);                   // elements per 16 bytes
+    const int dkp = (dk + V - 1) / V * V;               // the padding of a cache row is zero: whole 16-byte pieces are used
     float* qs = reinterpret_cast<float*>(smem_raw);
-    uint32_t* ks = reinterpret_cast<uint32_t*>(qs + HB * dk);
+    uint32_t* ks = reinterpret_cast<uint32_t*>(qs + HB * dkp);
     pdl_wait();
     const int t = blockIdx.y, split = blockIdx.x;
     const int p = positions[t];
-    const int k_lo = split * SPLIT;
+    const int k_lo = split * span;
     if (k_lo > p) return;
-    const int k_hi = min(k_lo + SPLIT - 1, p);          // inclusive
+    const int k_hi = min(k_lo + span - 1, p);           // inclusive
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h0 = blockIdx.z * HB, h = h0 + warp;
     const int nh = min(HB, H - h0);
-    for (int i = threadIdx.x; i < nh * dk; i += blockDim.x) qs[i] = qa[((size_t)t * H + h0) * dk + i];
     const int* bt = block_table + (size_t)token_seq[t] * bt_stride;
-    const int vec_per_row = row * (int)sizeof(T) / 16;   // rows are padded to multiples of 16 bytes
+    const int vec_per_row = row / V;                    // rows are padded to multiples of 16 bytes
+    auto stage = [&](int base, int buf) {
+        const int nk = min(32, k_hi - base + 1);
+        uint32_t* dst = ks + buf * 32 * kw;
+        for (int i = threadIdx.x; i < nk * vec_per_row; i += HB * 32) {
+            const int j = i / vec_per_row, v = i - j * vec_per_row;
+            const int pos = base + j;
+            const T* src = pages + ((size_t)bt[pos / ps] * ps + pos % ps) * row;
+            cp16(dst + j * kw + v * 4, reinterpret_cast<const unsigned char*>(src) + 16 * v);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(k_lo, 0);
+    for (int i = threadIdx.x; i < nh * dkp; i += blockDim.x) {
+        const int hh = i / dkp, d = i - hh * dkp;
+        qs[i] = d < dk ? qa[((size_t)t * H + h0 + hh) * dk + d] : 0.f;
+    }
     float m = -INFINITY, l = 0.f, acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-    const float* q = qs + warp * dk;
-    for (int base = k_lo; base <= k_hi; base += 32) {
-        __syncthreads();            // the queries are in; the last chunk has been used
+    const float* q = qs + warp * dkp;
+    int buf = 0;
+    for (int base = k_lo; base <= k_hi; base += 32, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();            // this chunk (and the queries) are in; the other buffer has been used
+        if (base + 32 <= k_hi) stage(base + 32, buf ^ 1);
         const int nk = min(32, k_hi - base + 1);
-        for (int i = threadIdx.x; i < nk * vec_per_row; i += blockDim.x) {
-            const int j = i / vec_per_row, v = i % vec_per_row;
-            const int pos = base + j;
-            const T* src = pages + ((size_t)bt[pos / ps] * ps + pos % ps) * row;
-            const uint4 x = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(src) + 16 * v);
-            uint32_t* dst = ks + j * kw + v * 4;
-            dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
-        }
-        __syncthreads();
         if (h >= H) continue;
+        const uint32_t* kc = ks + buf * 32 * kw;
         float s = -INFINITY;
         if (lane < nk) {
-            const uint32_t* kr = ks + lane * kw;
+            const uint32_t* kr = kc + lane * kw;
             float d0 = 0.f, d1 = 0.f;
-            if constexpr (sizeof(T) == 4) {
-                int d = 0;
-                for (; d + 1 < dk; d += 2) {
-                    d0 = fmaf(q[d], __uint_as_float(kr[d]), d0);
-                    d1 = fmaf(q[d + 1], __uint_as_float(kr[d + 1]), d1);
+            for (int d = 0; d < dkp; d += V) {
+                const uint4 kv = *reinterpret_cast<const uint4*>(kr + d / EPW);
+                const float4 qa0 = *reinterpret_cast<const float4*>(q + d);
+                if constexpr (sizeof(T) == 4) {
+                    d0 = fmaf(qa0.x, __uint_as_float(kv.x), d0);
+                    d1 = fmaf(qa0.y, __uint_as_float(kv.y), d1);
+                    d0 = fmaf(qa0.z, __uint_as_float(kv.z), d0);
+                    d1 = fmaf(qa0.w, __uint_as_float(kv.w), d1);
+                } else {
+                    const float4 qa1 = *reinterpret_cast<const float4*>(q + d + 4);
+                    d0 = fmaf(qa0.x, __uint_as_float(kv.x << 16), d0);
+                    d1 = fmaf(qa0.y, __uint_as_float(kv.x & 0xffff0000u), d1);
+                    d0 = fmaf(qa0.z, __uint_as_float(kv.y << 16), d0);
+                    d1 = fmaf(qa0.w, __uint_as_float(kv.y & 0xffff0000u), d1);
+                    d0 = fmaf(qa1.x, __uint_as_float(kv.z << 16), d0);
+                    d1 = fmaf(qa1.y, __uint_as_float(kv.z & 0xffff0000u), d1);
+                    d0 = fmaf(qa1.z, __uint_as_float(kv.w << 16), d0);
+                    d1 = fmaf(qa1.w, __uint_as_float(kv.w & 0xffff0000u), d1);
                 }
-                if (d < dk) d0 = fmaf(q[d], __uint_as_float(kr[d]), d0);
-            } else {
-                int d = 0;
-                for (; d + 1 < dk; d += 2) {
-                    const uint32_t w = kr[d >> 1];
-                    d0 = fmaf(q[d], __uint_as_float(w << 16), d0);
-                    d1 = fmaf(q[d + 1], __uint_as_float(w & 0xffff0000u), d1);
-                }
-                if (d < dk) d0 = fmaf(q[d], __uint_as_float(kr[d >> 1] << 16), d0);
             }
             s = (d0 + d1) * scale;
         }
@@ -197,17 +222,24 @@ latent_attention_kernel(const float* qa, const T* pages, int row, const int* blo
         m = m_new;
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
+        // the weighted sum: a lane owns the column pairs (2 * lane, 2 * lane + 1) + 64 * i
         for (int j = 0; j < nk; ++j) {
             const float w = __shfl_sync(0xffffffffu, pj, j);
-            const uint32_t* kr = ks + j * kw;
+            const uint32_t* kr = kc + j * kw;
 #pragma unroll
-            for (int i = 0; i < NACC; ++i) {
-                const int d = lane + 32 * i;
+            for (int i = 0; i < NACC / 2; ++i) {
+                const int d = 2 * lane + 64 * i;
                 if (d < R) {
-                    float c;
-                    if constexpr (sizeof(T) == 4) c = __uint_as_float(kr[d]);
-                    else c = __uint_as_float((d & 1) ? (kr[d >> 1] & 0xffff0000u) : (kr[d >> 1] << 16));
-                    acc[i] = fmaf(w, c, acc[i]);
+                    float c0, c1;
+                    if constexpr (sizeof(T) == 4) {
+                        const float2 c = *reinterpret_cast<const float2*>(kr + d);
+                        c0 = c.x; c1 = c.y;
+                    } else {
+                        const uint32_t c = kr[d >> 1];
+                        c0 = __uint_as_float(c << 16); c1 = __uint_as_float(c & 0xffff0000u);
+                    }
+                    acc[2 * i] = fmaf(w, c0, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(w, c1, acc[2 * i + 1]);
                 }
             }
         }
@@ -215,9 +247,10 @@ latent_attention_kernel(const float* qa, const T* pages, int row, const int* blo
     if (h >= H) return;
     const size_t o = ((size_t)t * H + h) * nsplit + split;
 #pragma unroll
-    for (int i = 0; i < NACC; ++i) {
-        const int d = lane + 32 * i;
-        if (d < R) part_o[o * R + d] = acc[i];
+    for (int i = 0; i < NACC / 2; ++i) {
+        const int d = 2 * lane + 64 * i;
+        if (d < R) part_o[o * R + d] = acc[2 * i];
+        if (d + 1 < R) part_o[o * R + d + 1] = acc[2 * i + 1];
     }
     if (lane == 0) {
         part_ml[o * 2] = m;
@@ -228,11 +261,11 @@ latent_attention_kernel(const float* qa, const T* pages, int row, const int* blo
 // One warp per (token, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M) over the splits the token has.
 __global__ void __launch_bounds__(256)
 latent_merge_kernel(const float* part_o, const float* part_ml, const int* positions, float* out, int nsplit, int TH, int H,
-                    int R) {
+                    int R, int span) {
     pdl_wait();
     const int th = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (th >= TH) return;
-    const int ns = positions[th / H] / SPLIT + 1;
+    const int ns = positions[th / H] / span + 1;
     const size_t o = (size_t)th * nsplit;
     float M = -INFINITY;
     for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(o + s) * 2]);
@@ -248,10 +281,10 @@ latent_merge_kernel(const float* part_o, const float* part_ml, const int* positi
 template <typename T, int NACC>
 int launch_attention(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* token_seq,
                      const int* positions, float* part_o, float* part_ml, int nsplit, int Tn, int H, int R, int dk,
-                     int ps, float scale, cudaStream_t stream) {
-    int kw = row * (int)sizeof(T) / 4;
-    kw |= 1;                                        // an odd row stride in words: lanes read their rows without bank conflicts
-    const size_t smem = (size_t)HB * dk * 4 + (size_t)32 * kw * 4;
+                     int ps, float scale, int span, cudaStream_t stream) {
+    const int kw = row * (int)sizeof(T) / 4 + 4;
+    const int V = 16 / (int)sizeof(T), dkp = (dk + V - 1) / V * V;
+    const size_t smem = (size_t)HB * dkp * 4 + (size_t)2 * 32 * kw * 4;
     static bool raised = false;                     // once per instantiation
     if (smem > 48 * 1024 && !raised) {
         MLLM_CUDA(cudaFuncSetAttribute(latent_attention_kernel<T, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -260,22 +293,22 @@ int launch_attention(const float* qa, const void* pages, int row, const int* bt,
     if (smem > 200 * 1024) return mllm_fail(1, "latent_attention: rows of %d need %zu bytes of shared memory", dk, smem);
     MLLM_CUDA(mllm_launch(latent_attention_kernel<T, NACC>, dim3(nsplit, Tn, (H + HB - 1) / HB), dim3(HB * 32), smem, stream,
                           true, qa, (const T*)pages, row, bt, bt_stride, token_seq, positions, part_o, part_ml, nsplit, H,
-                          R, dk, ps, scale, kw));
+                          R, dk, ps, scale, kw, span));
     return 0;
 }
 
 template <typename T>
 int pick_attention(int R, const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* token_seq,
                    const int* positions, float* part_o, float* part_ml, int nsplit, int Tn, int H, int dk, int ps,
-                   float scale, cudaStream_t stream) {
+                   float scale, int span, cudaStream_t stream) {
     if (R <= 128)
         return launch_attention<T, 4>(qa, pages, row, bt, bt_stride, token_seq, positions, part_o, part_ml, nsplit, Tn, H, R,
-                                      dk, ps, scale, stream);
+                                      dk, ps, scale, span, stream);
     if (R <= 256)
         return launch_attention<T, 8>(qa, pages, row, bt, bt_stride, token_seq, positions, part_o, part_ml, nsplit, Tn, H, R,
-                                      dk, ps, scale, stream);
+                                      dk, ps, scale, span, stream);
     return launch_attention<T, 16>(qa, pages, row, bt, bt_stride, token_seq, positions, part_o, part_ml, nsplit, Tn, H, R, dk,
-                                   ps, scale, stream);
+                                   ps, scale, span, stream);
 }
 
 
@@ -488,8 +521,6 @@ int launch_mma(const float* qa, const void* pages, int row, const int* bt, int b
 
 }  // namespace
 
-MLLM_EXPORT int mllm_latent_split_keys() { return SPLIT; }
-
 // proj [T, ...] in `dtype` with row stride ld: queries at column q_off (H heads of dn + dr), the down-projection at
 // dkv_off (R + dr columns; -1: this layer writes no cache row).  pages [slots][row] in `dtype`.  qa [T][H][R + dr] 32-bit:
 // only its columns R.. are written here.
@@ -541,28 +572,29 @@ MLLM_EXPORT int mllm_headwise_linear(const void* in, long long ld_in, int in_hea
 }
 
 // qa [T][H][dk] 32-bit, pages [slots][row] in `dtype` (a token's row: R latent columns, then dk - R rotated key columns),
-// out [T][H][R] 32-bit; part_o [T * H * nsplit * R], part_ml [T * H * nsplit * 2] scratch; nsplit >= ceil(longest context / 256).
+// out [T][H][R] 32-bit; part_o [T * H * nsplit * R], part_ml [T * H * nsplit * 2] scratch; nsplit >= ceil(longest context / span).
 MLLM_EXPORT int mllm_latent_attention(const float* qa, const void* pages, int row, const int* block_table, int bt_stride,
                                       const int* token_seq, const int* positions, float* part_o, float* part_ml, int nsplit,
-                                      float* out, int Tn, int H, int R, int dk, int ps, float scale, int dtype,
+                                      float* out, int Tn, int H, int R, int dk, int ps, float scale, int span, int dtype,
                                       cudaStream_t stream) {
     if (Tn <= 0) return 0;
     if (R <= 0 || R > MAX_R || dk < R || dk > MAX_DK) return mllm_fail(1, "latent_attention: latent size %d (at most %d), key size %d (at most %d)", R, MAX_R, dk, MAX_DK);
     const int es = dtype == MLLM_F32 ? 4 : 2;
     if (row < dk || (row * es) % 16 != 0 || (uintptr_t)pages % 16 != 0) return mllm_fail(1, "latent_attention: cache rows of %d elements must hold %d and be multiples of 16 bytes", row, dk);
     if (Tn > 65535) return mllm_fail(1, "latent_attention: more than 65535 tokens in a step");
+    if (span < 32 || span % 32) return mllm_fail(1, "latent_attention: a split of %d keys (a multiple of 32)", span);
     int rc;
     if (dtype == MLLM_F32)
         rc = pick_attention<float>(R, qa, pages, row, block_table, bt_stride, token_seq, positions, part_o, part_ml, nsplit, Tn,
-                                   H, dk, ps, scale, stream);
+                                   H, dk, ps, scale, span, stream);
     else if (dtype == MLLM_BF16)
         rc = pick_attention<__nv_bfloat16>(R, qa, pages, row, block_table, bt_stride, token_seq, positions, part_o, part_ml,
-                                           nsplit, Tn, H, dk, ps, scale, stream);
+                                           nsplit, Tn, H, dk, ps, scale, span, stream);
     else
         return mllm_fail(1, "latent_attention: unknown dtype code %d", dtype);
     if (rc) return rc;
     MLLM_CUDA(mllm_launch(latent_merge_kernel, dim3((Tn * H + 7) / 8), dim3(256), 0, stream, true, part_o, part_ml, positions,
-                          out, nsplit, Tn * H, H, R));
+                          out, nsplit, Tn * H, H, R, span));
     return 0;
 }
 

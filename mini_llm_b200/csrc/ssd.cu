@@ -5,7 +5,7 @@
 //                      be cut anywhere.  conv_state_update then stores the last taps - 1 inputs of every request.
 //   ssd_scan           per request and head: dt = softplus(raw + bias), S <- exp(-exp(A_log) dt) S + dt B x^T,
 //                      y = S^T C + D x, token by token.  A CTA owns 32 columns of a head's state S [N, P]; a warp owns 4
-//                      columns, its lanes 8 row groups (rows rg, rg + 8, ...), so a thread keeps N / 8 state elements
+//                      columns, its lanes 8 row groups of consecutive rows, so a thread keeps N / 8 state elements
 //                      in registers and the sum over rows ends in three shuffles.  Tokens are staged 16 at a time.
 //                      Every state element is a recurrence of its own, so the state after n tokens is the same bits
 //                      however the n tokens were cut into steps.
@@ -20,6 +20,10 @@ constexpr int CHUNK = 16;
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ void cp4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
 
 // grid: blocks of 256 over (token, channel).  u = proj[:, off : off + C]; state [slots][stride], the conv part at
 // conv_off: [taps - 1][C], oldest first.
@@ -71,18 +75,19 @@ conv_state_update_kernel(const T* proj, long long ld, int off, float* state, lon
 
 // grid (column blocks of 32, heads, requests), 256 threads.  xbc [T][C] 32-bit (x at 0, B at b_off, C at c_off);
 // dt_raw = proj[:, dt_off + head] in the activation dtype; state [slots][stride] with S of head h at h * N * P, [N][P].
+// Thread (column, rg) owns the ROWS consecutive state rows rg * ROWS ..: it reads its part of B_t and C_t with 16-byte
+// loads (a token's B and C are staged with 4 floats of padding after every ROWS rows, so the eight row groups fall on
+// different banks; rows beyond N are staged as zeros and stay zero in the state).
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(256)
 ssd_scan_kernel(const float* xbc, int Cw, int b_off, int c_off, const T* proj, long long ld, int dt_off,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dh,
                 float* state, long long state_stride, const int* cu_q, const int* slots, float* y, int Hm, int N, int P,
                 int G, int write_state) {
-    extern __shared__ float sm[];
-    float* Bs = sm;                         // [CHUNK][N]
-    float* Cs = Bs + CHUNK * N;             // [CHUNK][N]
-    float* xs = Cs + CHUNK * N;             // [CHUNK][32]
-    float* dts = xs + CHUNK * 32;           // [CHUNK]
-    float* das = dts + CHUNK;               // [CHUNK]
+    constexpr int PAD = ROWS == 4 ? 0 : 4;
+    constexpr int NP = 8 * (ROWS + PAD);    // floats of a token's B (or C) in shared memory
+    extern __shared__ __align__(16) float sm[];
+    // two buffers of: B [CHUNK][NP], C [CHUNK][NP], x [CHUNK][32], dt [CHUNK], decay [CHUNK]
     pdl_wait();
     const int h = blockIdx.y, s = blockIdx.z, j0 = blockIdx.x * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,53 +99,92 @@ ssd_scan_kernel(const float* xbc, int Cw, int b_off, int c_off, const T* proj, l
     float st[ROWS];
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
-        const int r = rg + 8 * i;
+        const int r = rg * ROWS + i;
         st[i] = (live && r < N) ? S[(size_t)r * P + col] : 0.f;
     }
     const float a = -expf(A_log[h]), dskip = Dh[h], dtb = dt_bias[h];
-    for (int c0 = 0; c0 < n; c0 += CHUNK) {
+    constexpr int BUF = 2 * CHUNK * NP + CHUNK * 32 + 2 * CHUNK;     // floats of one chunk's buffer
+    // a chunk's B, C and x come in by 4-byte cp.async while the chunk before it is walked; its step sizes are read into
+    // a register at the same time and turned into dt and the decay after the walk
+    float raw_dt = 0.f;
+    auto stage = [&](int c0, int buf) {
         const int nc = min(CHUNK, n - c0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nc * N; i += 256) {
-            const int tt = i / N, r = i % N;
+        float* B2 = sm + buf * BUF;
+        float* C2 = B2 + CHUNK * NP;
+        float* x2 = C2 + CHUNK * NP;
+        for (int i = threadIdx.x; i < nc * 8 * ROWS; i += 256) {
+            const int tt = i / (8 * ROWS), r = i - tt * 8 * ROWS;
             const float* rowp = xbc + (size_t)(t0 + c0 + tt) * Cw;
-            Bs[tt * N + r] = rowp[b_off + g * N + r];
-            Cs[tt * N + r] = rowp[c_off + g * N + r];
+            const int at = tt * NP + r + (r / ROWS) * PAD;
+            if (r < N) {
+                cp4(B2 + at, rowp + b_off + g * N + r);
+                cp4(C2 + at, rowp + c_off + g * N + r);
+            } else {
+                B2[at] = 0.f;
+                C2[at] = 0.f;
+            }
         }
         for (int i = threadIdx.x; i < nc * 32; i += 256) {
             const int tt = i >> 5, c = i & 31;
-            xs[i] = j0 + c < P ? xbc[(size_t)(t0 + c0 + tt) * Cw + (size_t)h * P + j0 + c] : 0.f;
+            if (j0 + c < P) cp4(x2 + i, xbc + (size_t)(t0 + c0 + tt) * Cw + (size_t)h * P + j0 + c);
+            else x2[i] = 0.f;
         }
-        if (threadIdx.x < nc) {
-            const float dt = softplus_f(to_f32(proj[(size_t)(t0 + c0 + threadIdx.x) * ld + dt_off + h]) + dtb);
-            dts[threadIdx.x] = dt;
-            das[threadIdx.x] = expf(a * dt);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (threadIdx.x < nc) raw_dt = to_f32(proj[(size_t)(t0 + c0 + threadIdx.x) * ld + dt_off + h]);
+    };
+    auto steps = [&](int c0, int buf) {
+        if (threadIdx.x < min(CHUNK, n - c0)) {
+            float* d2 = sm + buf * BUF + 2 * CHUNK * NP + CHUNK * 32;
+            const float dt = softplus_f(raw_dt + dtb);
+            d2[threadIdx.x] = dt;
+            d2[CHUNK + threadIdx.x] = expf(a * dt);
         }
-        __syncthreads();
+    };
+    if (n > 0) {
+        stage(0, 0);
+        steps(0, 0);
+    }
+    for (int c0 = 0, buf = 0; c0 < n; c0 += CHUNK, buf ^= 1) {
+        const int nc = min(CHUNK, n - c0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                    // this chunk is in; the other buffer has been walked
+        const bool more = c0 + CHUNK < n;
+        if (more) stage(c0 + CHUNK, buf ^ 1);
+        const float* Bs = sm + buf * BUF;
+        const float* Cs = Bs + CHUNK * NP;
+        const float* xs = Cs + CHUNK * NP;
+        const float* dts = xs + CHUNK * 32;
+        const float* das = dts + CHUNK;
         for (int tt = 0; tt < nc; ++tt) {
             const float dt = dts[tt], da = das[tt], xv = xs[tt * 32 + warp * 4 + (lane >> 3)];
             const float dx = dt * xv;
-            const float* Bt = Bs + tt * N;
-            const float* Ct = Cs + tt * N;
-            float acc = 0.f;
+            const float4* Bt = reinterpret_cast<const float4*>(Bs + tt * NP + rg * (ROWS + PAD));
+            const float4* Ct = reinterpret_cast<const float4*>(Cs + tt * NP + rg * (ROWS + PAD));
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;        // four partial sums: the order is fixed, the chain short
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int r = rg + 8 * i;
-                if (r < N) {
-                    st[i] = fmaf(da, st[i], Bt[r] * dx);
-                    acc = fmaf(st[i], Ct[r], acc);
-                }
+            for (int i = 0; i < ROWS / 4; ++i) {
+                const float4 b = Bt[i], c = Ct[i];
+                st[4 * i] = fmaf(da, st[4 * i], b.x * dx);
+                a0 = fmaf(st[4 * i], c.x, a0);
+                st[4 * i + 1] = fmaf(da, st[4 * i + 1], b.y * dx);
+                a1 = fmaf(st[4 * i + 1], c.y, a1);
+                st[4 * i + 2] = fmaf(da, st[4 * i + 2], b.z * dx);
+                a2 = fmaf(st[4 * i + 2], c.z, a2);
+                st[4 * i + 3] = fmaf(da, st[4 * i + 3], b.w * dx);
+                a3 = fmaf(st[4 * i + 3], c.w, a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (rg == 0 && live) y[(size_t)(t0 + c0 + tt) * ((size_t)Hm * P) + (size_t)h * P + col] = fmaf(dskip, xv, acc);
         }
+        if (more) steps(c0 + CHUNK, buf ^ 1);
     }
     if (write_state && live) {
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-            const int r = rg + 8 * i;
+            const int r = rg * ROWS + i;
             if (r < N) S[(size_t)r * P + col] = st[i];
         }
     }
@@ -234,8 +278,9 @@ MLLM_EXPORT int mllm_ssd_scan(const float* xbc, int Cw, int b_off, int c_off, co
     if (G < 1 || Hm % G) return mllm_fail(1, "ssd_scan: %d heads in %d groups", Hm, G);
     if (S > 65535 || Hm > 65535) return mllm_fail(1, "ssd_scan: grid too large");
     const dim3 grid((P + 31) / 32, Hm, S);
-    const size_t smem = ((size_t)2 * CHUNK * N + CHUNK * 32 + 2 * CHUNK) * sizeof(float);
     const int rows = (N + 7) / 8;
+    const int rpt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;            // the instantiation's rows per thread
+    const size_t smem = 2 * ((size_t)2 * CHUNK * 8 * (rpt + (rpt == 4 ? 0 : 4)) + CHUNK * 32 + 2 * CHUNK) * sizeof(float);
     if (dtype == MLLM_F32)
         return scan_launch<float>(rows, grid, smem, stream, xbc, Cw, b_off, c_off, proj, ld, dt_off, dt_bias, A_log, Dh, state,
                                   state_stride, cu_q, slots, y, Hm, N, P, G, write_state);

@@ -107,7 +107,7 @@ def _signatures(lib):
         "mllm_headwise_linear": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_void_p],
         "mllm_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_latent_attention_mma": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_float, c_void_p],
         "mllm_latent_mma_ok": [c_int, c_int, c_int],
@@ -872,7 +872,9 @@ def norm_scale_add(y, weight, scale, x, eps: float) -> None:
 
 # --------------------------------------------------------------------------- attention over a cache of latents
 LATENT_MAX_RANK, LATENT_MAX_KEY = 512, 1024      # what csrc/latent_attention.cu takes
-_latent_split_keys = None
+# keys per CTA of the CUDA-core kernel: short splits when a step has single tokens only (a few long contexts must fill
+# the GPU), long ones when it has prompt portions (their tokens fill it, and every split costs a partial result)
+LATENT_SPAN_DECODE, LATENT_SPAN_PROMPT = 128, 1024
 
 
 def latent_prepare(proj, q_off: int, dkv_off: Optional[int], ctx, slot_mapping, freq, mscale: float, norm_weight, eps: float,
@@ -935,7 +937,6 @@ def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int,
     out[t, h] = sum_j softmax_j((qa[t, h] . row_j[:dk]) * scale) row_j[:rank], 32-bit [T, heads * rank].
     ``impl``: "split" (CUDA cores, all 32-bit, splits of 256 keys: single tokens, 32-bit caches, any size) or "mma"
     (tensor cores: steps with prompt portions over a bfloat16 cache); None picks by the step's shape."""
-    global _latent_split_keys
     _cuda("qa", qa, torch.float32)
     _cuda("pages", pages)
     _cuda("out", out, torch.float32)
@@ -961,25 +962,21 @@ def latent_attention(qa, pages, block_table, ctx, out, *, heads: int, rank: int,
         return
     if impl != "split":
         raise KernelError(f"latent_attention: unknown implementation {impl!r}")
-    if _latent_split_keys is None:
-        _latent_split_keys = int(library().mllm_latent_split_keys())
-    need = max(1, -(-int(ctx.max_ctx_len) // _latent_split_keys))
+    span = LATENT_SPAN_DECODE if getattr(ctx, "decode_only", False) else LATENT_SPAN_PROMPT
+    need = max(1, -(-int(ctx.max_ctx_len) // span))
     nsplit = 1 << (need - 1).bit_length()       # a power of two: few distinct grids for captured graphs
     part_o = ctx.ws.buf("latent_part_o", T * heads * nsplit, rank, torch.float32)
     part_ml = ctx.ws.buf("latent_part_ml", T * heads * nsplit, 2, torch.float32)
     _call("mllm_latent_attention", qa.data_ptr(), pages.data_ptr(), row, block_table.data_ptr(), _rows("block_table", block_table),
           ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), nsplit, out.data_ptr(),
-          T, heads, rank, dk, ps, float(scale), _dt(pages), _stream())
+          T, heads, rank, dk, ps, float(scale), span, _dt(pages), _stream())
     global launches
     launches += 1           # the kernel that merges the splits
 
 
 def latent_splits(max_ctx_len: int) -> int:
     """Splits of the latent attention at a context length (part of a step's shape for captured graphs)."""
-    global _latent_split_keys
-    if _latent_split_keys is None:
-        _latent_split_keys = int(library().mllm_latent_split_keys())
-    need = max(1, -(-int(max_ctx_len) // _latent_split_keys))
+    need = max(1, -(-int(max_ctx_len) // LATENT_SPAN_DECODE))
     return 1 << (need - 1).bit_length()
 
 
