@@ -3,7 +3,8 @@
 //   moe_route       a warp per token: router logits in 32-bit, softmax over all experts, the best `keep` of `n_groups`
 //                   equal groups of neighbouring experts (a group's score is its largest), the `top` best experts inside
 //                   those groups (the lowest index wins among equals), weights = scores / (their sum + 1e-20).
-//   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets.
+//   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets;
+//                   with up to 16 tokens (decode steps) routing and ordering are one launch of one CTA.
 //   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e; a CTA finds its expert from the offsets on the
 //                   device, so the grid depends on the number of pairs only.  `gated`: W_e is [2F, K] (gate rows, then
 //                   up rows) and the result is silu(gate) * up.  Three kernels: CUDA cores, 32 pairs x 64 columns per
@@ -16,19 +17,13 @@
 namespace {
 
 constexpr int MAX_E = 512;
+constexpr int MOE_FEW_TOKENS = 16;    // up to this many tokens one CTA routes them all and orders the pairs in the same launch
 constexpr int MOE_FEW_PAIRS = 32;     // up to this many (token, choice) pairs every pair streams its expert's weights itself
 
+// One warp routes one token; `s` is the warp's E floats of shared memory.
 template <typename T>
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups, int keep,
-                 int* idx, float* wout) {
-    __shared__ float sc[4][MAX_E];
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= Tn) return;
-    float* s = sc[warp];
-    const T* x = h + (size_t)t * ld;
+__device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr, float* s, int D, int E, int top, int n_groups,
+                                            int keep, int* idx, float* wout, int lane) {
     for (int e = 0; e < E; ++e) {
         const T* w = Wr + (size_t)e * D;
         float a = 0.f;
@@ -50,45 +45,45 @@ moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int
     __syncwarp();
     for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
     __syncwarp();
-    if (lane != 0) return;
-    // experts outside the kept groups are marked by a negative score (scores are >= 0)
-    if (n_groups > 1 && keep < n_groups) {
-        const int per = E / n_groups;
-        unsigned long long kept_lo = 0ull;          // groups are few: a bit set over up to 64 of them, else a scan
-        for (int k = 0; k < keep; ++k) {
-            int best = -1;
-            float bv = -1.f;
-            for (int g = 0; g < n_groups; ++g) {
-                if (g < 64 && ((kept_lo >> g) & 1ull)) continue;
-                float gm = -1.f;
-                for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
-                if (gm > bv) { bv = gm; best = g; }
+    if (lane == 0) {
+        // experts outside the kept groups are marked by a negative score (scores are >= 0)
+        if (n_groups > 1 && keep < n_groups) {
+            const int per = E / n_groups;
+            unsigned long long kept = 0ull;                 // at most 64 groups
+            for (int k = 0; k < keep; ++k) {
+                int best = -1;
+                float bv = -1.f;
+                for (int g = 0; g < n_groups; ++g) {
+                    if ((kept >> g) & 1ull) continue;
+                    float gm = -1.f;
+                    for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
+                    if (gm > bv) { bv = gm; best = g; }
+                }
+                if (best >= 0) kept |= 1ull << best;
             }
-            if (best >= 0) kept_lo |= 1ull << best;
+            for (int g = 0; g < n_groups; ++g)
+                if (!((kept >> g) & 1ull))
+                    for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -1.f - s[e];
         }
-        for (int g = 0; g < n_groups; ++g)
-            if (!((kept_lo >> g) & 1ull))
-                for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -1.f - s[e];
+        float wsum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (s[e] > bv) { bv = s[e]; best = e; }
+            idx[k] = best;
+            wout[k] = bv;
+            wsum += bv;
+            s[best] = -8.f;                                  // taken
+        }
+        for (int k = 0; k < top; ++k) wout[k] = wout[k] / (wsum + 1e-20f);
     }
-    float wsum = 0.f;
-    for (int k = 0; k < top; ++k) {
-        int best = 0;
-        float bv = -INFINITY;
-        for (int e = 0; e < E; ++e)
-            if (s[e] > bv) { bv = s[e]; best = e; }
-        idx[(size_t)t * top + k] = best;
-        wout[(size_t)t * top + k] = bv;
-        wsum += bv;
-        s[best] = -8.f;                              // taken
-    }
-    for (int k = 0; k < top; ++k) wout[(size_t)t * top + k] = wout[(size_t)t * top + k] / (wsum + 1e-20f);
+    __syncwarp();
 }
 
-// one CTA of 1024 threads: offsets[E + 1], sorted[n] = pair ids ordered by expert (pairs of one expert in pair order)
-__global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
-    __shared__ int cnt[MAX_E + 1];
-    pdl_wait();
+// The (token, choice) pairs ordered by expert: offsets[E + 1], sorted[n] = pair ids (pairs of one expert in pair order).
+// All threads of the CTA; cnt holds E + 1 ints of shared memory.
+__device__ __forceinline__ void sort_pairs(const int* idx, int n, int E, int* offsets, int* sorted, int* cnt) {
     for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
@@ -116,6 +111,43 @@ moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
             at += __popc(ballot);
         }
     }
+}
+
+// 4 warps, a token each; dynamic shared memory: 4 * E floats
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups, int keep,
+                 int* idx, float* wout) {
+    extern __shared__ float sc[];
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= Tn) return;
+    route_token(h + (size_t)t * ld, Wr, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top, wout + (size_t)t * top, lane);
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
+    __shared__ int cnt[MAX_E + 1];
+    pdl_wait();
+    sort_pairs(idx, n, E, offsets, sorted, cnt);
+}
+
+// Few tokens (decode steps): one CTA of 8 warps routes them all and orders the pairs, in one launch.
+// dynamic shared memory: 8 * E floats, then E + 1 ints
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_sort_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups,
+                      int keep, int* idx, float* wout, int* offsets, int* sorted) {
+    extern __shared__ float sc[];
+    int* cnt = reinterpret_cast<int*>(sc + 8 * E);
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t = warp; t < Tn; t += 8)
+        route_token(h + (size_t)t * ld, Wr, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
+                    wout + (size_t)t * top, lane);
+    __syncthreads();                                         // the CTA's own writes of idx are visible to all its threads
+    sort_pairs(idx, Tn * top, E, offsets, sorted, cnt);
 }
 
 template <typename TA, typename TW, typename TO>
@@ -412,17 +444,33 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int 
     if (n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || n_groups > 64)
         return mllm_fail(1, "moe_route: %d experts in %d groups (at most 64), %d kept", E, n_groups, keep);
     if (keep * (E / n_groups) < top) return mllm_fail(1, "moe_route: %d kept groups of %d experts cannot give %d", keep, E / n_groups, top);
+    if (Tn <= MOE_FEW_TOKENS) {
+        const size_t smem = (size_t)8 * E * 4 + (size_t)(E + 1) * 4;
+        if (dtype == MLLM_F32)
+            MLLM_CUDA(mllm_launch(moe_route_sort_kernel<float>, dim3(1), dim3(256), smem, stream, true, (const float*)h, ld,
+                                  (const float*)Wr, Tn, D, E, top, n_groups, keep, idx, w, offsets, sorted));
+        else if (dtype == MLLM_BF16)
+            MLLM_CUDA(mllm_launch(moe_route_sort_kernel<__nv_bfloat16>, dim3(1), dim3(256), smem, stream, true,
+                                  (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, Tn, D, E, top, n_groups, keep, idx, w,
+                                  offsets, sorted));
+        else
+            return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
+        return 0;
+    }
+    const size_t smem = (size_t)4 * E * 4;
     if (dtype == MLLM_F32)
-        MLLM_CUDA(mllm_launch(moe_route_kernel<float>, dim3((Tn + 3) / 4), dim3(128), 0, stream, true, (const float*)h, ld,
+        MLLM_CUDA(mllm_launch(moe_route_kernel<float>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true, (const float*)h, ld,
                               (const float*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
     else if (dtype == MLLM_BF16)
-        MLLM_CUDA(mllm_launch(moe_route_kernel<__nv_bfloat16>, dim3((Tn + 3) / 4), dim3(128), 0, stream, true,
+        MLLM_CUDA(mllm_launch(moe_route_kernel<__nv_bfloat16>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true,
                               (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
     else
         return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
     MLLM_CUDA(mllm_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, true, (const int*)idx, Tn * top, E, offsets, sorted));
     return 0;
 }
+
+MLLM_EXPORT int mllm_moe_few_tokens() { return MOE_FEW_TOKENS; }
 
 // kind 0: A in `dtype`, gated, out in `dtype` (the experts' first product with its activation);
 // kind 1: A in `dtype`, out 32-bit (the experts' second product).

@@ -121,34 +121,68 @@ gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long lon
     }
 }
 
-// x[r] += (y[r] / sqrt(mean(y[r]^2) + eps) * w) * ls: a branch's result, normed, scaled per column and added to the
-// 32-bit residual stream in one pass (ls may be absent).
+// x[r] += (v / sqrt(mean(v^2) + eps) * w) * ls with v = y[r] (+ sum_k pw[r][k] * pairs[r * top + k], the weighted
+// results of a routed feed-forward's chosen experts, in the order of k): a branch's result, normed, scaled per column and
+// added to the 32-bit residual stream in one pass (ls, y or the pairs may be absent).  With `nw` the new x is normed once
+// more, h = x / sqrt(mean(x^2) + neps) * (nw + noff), for the branch that reads it next.  The row is kept in shared memory.
+template <typename TOut>
 __global__ void __launch_bounds__(256)
-norm_scale_add_kernel(const float* y, long long y_stride, const float* __restrict__ w, const float* __restrict__ ls, float* x,
-                      long long x_stride, int D, float eps) {
+join_kernel(const float* y, long long y_stride, const float* pairs, const float* pw, int top, const float* __restrict__ w,
+            const float* __restrict__ ls, float* x, long long x_stride, const float* __restrict__ nw, float noff, float neps,
+            TOut* h, long long h_stride, int D, float eps) {
+    extern __shared__ float rowbuf[];       // [D]
     __shared__ float scratch[33];
     pdl_wait();
     pdl_launch();
-    const float* yr = y + (size_t)blockIdx.x * y_stride;
-    float* xr = x + (size_t)blockIdx.x * x_stride;
+    const size_t r = blockIdx.x;
+    float* xr = x + r * x_stride;
     float q = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) q = fmaf(yr[d], yr[d], q);
-    const float r = sqrtf(block_sum(q, scratch) / (float)D + eps);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float v = yr[d] / r * w[d];
-        if (ls) v *= ls[d];
-        xr[d] += v;
+        float v = y ? y[r * y_stride + d] : 0.f;
+        if (pairs)
+            for (int k = 0; k < top; ++k) v = fmaf(pw[r * top + k], pairs[(r * top + k) * D + d], v);
+        rowbuf[d] = v;
+        q = fmaf(v, v, q);
     }
+    const float rr = sqrtf(block_sum(q, scratch) / (float)D + eps);
+    float q2 = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = rowbuf[d] / rr * w[d];
+        if (ls) v *= ls[d];
+        v += xr[d];
+        xr[d] = v;
+        rowbuf[d] = v;
+        q2 = fmaf(v, v, q2);
+    }
+    if (!nw) return;
+    const float r2 = sqrtf(block_sum(q2, scratch) / (float)D + neps);
+    TOut* hr = h + r * h_stride;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = from_f32<TOut>(rowbuf[d] / r2 * (nw[d] + noff));
 }
 
 }  // namespace
 
-MLLM_EXPORT int mllm_norm_scale_add(const float* y, long long y_stride, const float* w, const float* ls, float* x,
-                                    long long x_stride, int R, int D, float eps, cudaStream_t stream) {
+MLLM_EXPORT int mllm_norm_scale_add(const float* y, long long y_stride, const float* pairs, const float* pw, int top,
+                                    const float* w, const float* ls, float* x, long long x_stride, const float* nw,
+                                    float noff, float neps, void* h, long long h_stride, int R, int D, float eps,
+                                    int h_dtype, cudaStream_t stream) {
     if (R <= 0) return 0;
-    if (D <= 0) return mllm_fail(1, "norm_scale_add: width %d", D);
+    if (D <= 0 || (size_t)D * 4 > 200 * 1024) return mllm_fail(1, "norm_scale_add: width %d", D);
+    if (!y && !pairs) return mllm_fail(1, "norm_scale_add: neither a result nor pairs to add");
     const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
-    MLLM_CUDA(mllm_launch(norm_scale_add_kernel, dim3(R), dim3(threads), 0, stream, true, y, y_stride, w, ls, x, x_stride, D, eps));
+    const size_t smem = (size_t)D * 4;
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        MLLM_CUDA(cudaFuncSetAttribute(join_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        MLLM_CUDA(cudaFuncSetAttribute(join_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    if (nw && h_dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(join_kernel<__nv_bfloat16>, dim3(R), dim3(threads), smem, stream, true, y, y_stride, pairs, pw, top,
+                              w, ls, x, x_stride, nw, noff, neps, (__nv_bfloat16*)h, h_stride, D, eps));
+    else
+        MLLM_CUDA(mllm_launch(join_kernel<float>, dim3(R), dim3(threads), smem, stream, true, y, y_stride, pairs, pw, top, w, ls,
+                              x, x_stride, nw, noff, neps, (float*)h, h_stride, D, eps));
     return 0;
 }
 

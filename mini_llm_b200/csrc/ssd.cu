@@ -25,28 +25,64 @@ __device__ __forceinline__ void cp4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// grid: blocks of 256 over (token, channel).  u = proj[:, off : off + C]; state [slots][stride], the conv part at
-// conv_off: [taps - 1][C], oldest first.
+// grid (channel blocks of 256, tokens).  u = proj[:, off : off + C]; state [slots][stride], the conv part at conv_off:
+// [taps - 1][C], oldest first.
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_silu_kernel(const T* proj, long long ld, int off, const float* __restrict__ w, const float* __restrict__ bias,
                  const float* state, long long state_stride, int conv_off, const int* token_seq, const int* cu_q,
                  const int* slots, float* out, int Tn, int C, int taps) {
     pdl_wait();
-    const long long total = (long long)Tn * C;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int t = (int)(i / C), ch = (int)(i % C);
-        const int s = token_seq[t];
-        const int qi = t - cu_q[s];
+    const int t = blockIdx.y, ch = blockIdx.x * 256 + threadIdx.x;
+    if (ch >= C) return;
+    const int s = token_seq[t];
+    const int qi = t - cu_q[s];
+    float acc = bias[ch];
+    if (qi >= taps - 1) {                   // every input lies in this step
+        for (int j = 0; j < taps; ++j)
+            acc = fmaf(w[(size_t)ch * taps + j], to_f32(proj[(size_t)(t - (taps - 1) + j) * ld + off + ch]), acc);
+    } else {
         const float* st = state + (size_t)slots[s] * state_stride + conv_off;
-        float acc = bias[ch];
         for (int j = 0; j < taps; ++j) {
             const int src = qi - (taps - 1) + j;
             const float u = src >= 0 ? to_f32(proj[(size_t)(t - (taps - 1) + j) * ld + off + ch])
                                      : st[(size_t)(taps - 1 + src) * C + ch];
             acc = fmaf(w[(size_t)ch * taps + j], u, acc);
         }
-        out[(size_t)t * C + ch] = silu_f(acc);
+    }
+    out[(size_t)t * C + ch] = silu_f(acc);
+}
+
+// Steps in which every request brings one token: grid (channel blocks, requests); a thread computes its channel's output
+// from the state and the token, and shifts the token into the state (one launch instead of two).
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_step_kernel(const T* proj, long long ld, int off, const float* __restrict__ w, const float* __restrict__ bias,
+                 float* state, long long state_stride, int conv_off, const int* cu_q, const int* slots, float* out, int C,
+                 int taps, int write_state) {
+    pdl_wait();
+    const int ch = blockIdx.x * 256 + threadIdx.x, s = blockIdx.y;
+    if (ch >= C) return;
+    const int t = cu_q[s];
+    float* st = state + (size_t)slots[s] * state_stride + conv_off;
+    const float u = to_f32(proj[(size_t)t * ld + off + ch]);
+    float acc = bias[ch];
+    float keep[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) {
+        if (k < taps - 1) {
+            keep[k] = st[(size_t)k * C + ch];
+            acc = fmaf(w[(size_t)ch * taps + k], keep[k], acc);
+        }
+    }
+    acc = fmaf(w[(size_t)ch * taps + taps - 1], u, acc);
+    out[(size_t)t * C + ch] = silu_f(acc);
+    if (write_state) {
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) {
+            if (k + 1 < taps - 1) st[(size_t)k * C + ch] = keep[k + 1];
+            else if (k + 1 == taps - 1) st[(size_t)k * C + ch] = u;
+        }
     }
 }
 
@@ -247,17 +283,28 @@ MLLM_EXPORT int mllm_ssd_conv(const void* proj, long long ld, int off, const flo
                               float* out, int Tn, int S, int C, int taps, int write_state, int dtype, cudaStream_t stream) {
     if (Tn <= 0 || C <= 0) return 0;
     if (taps < 1 || taps > MAX_TAPS) return mllm_fail(1, "ssd_conv: %d taps (1 to %d)", taps, MAX_TAPS);
-    const long long total = (long long)Tn * C;
-    const int grid = (int)((total + 255) / 256 < 16384 ? (total + 255) / 256 : 16384);
+    if (Tn > 65535 || S > 65535) return mllm_fail(1, "ssd_conv: more than 65535 tokens in a step");
+    const dim3 grid((C + 255) / 256, Tn);
     const dim3 ugrid((C + 255) / 256, S);
+    const bool single = Tn == S;            // one token per request: output and state update in one launch
     if (dtype == MLLM_F32) {
-        MLLM_CUDA(mllm_launch(conv_silu_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)proj, ld, off, w, bias,
+        if (single) {
+            MLLM_CUDA(mllm_launch(conv_step_kernel<float>, ugrid, dim3(256), 0, stream, true, (const float*)proj, ld, off, w, bias,
+                                  state, state_stride, conv_off, cu_q, slots, out, C, taps, write_state));
+            return 0;
+        }
+        MLLM_CUDA(mllm_launch(conv_silu_kernel<float>, grid, dim3(256), 0, stream, true, (const float*)proj, ld, off, w, bias,
                               (const float*)state, state_stride, conv_off, token_seq, cu_q, slots, out, Tn, C, taps));
         if (write_state && taps > 1)
             MLLM_CUDA(mllm_launch(conv_state_update_kernel<float>, ugrid, dim3(256), 0, stream, true, (const float*)proj, ld, off,
                                   state, state_stride, conv_off, cu_q, slots, C, taps));
     } else if (dtype == MLLM_BF16) {
-        MLLM_CUDA(mllm_launch(conv_silu_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)proj,
+        if (single) {
+            MLLM_CUDA(mllm_launch(conv_step_kernel<__nv_bfloat16>, ugrid, dim3(256), 0, stream, true, (const __nv_bfloat16*)proj, ld,
+                                  off, w, bias, state, state_stride, conv_off, cu_q, slots, out, C, taps, write_state));
+            return 0;
+        }
+        MLLM_CUDA(mllm_launch(conv_silu_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, (const __nv_bfloat16*)proj,
                               ld, off, w, bias, (const float*)state, state_stride, conv_off, token_seq, cu_q, slots, out, Tn, C,
                               taps));
         if (write_state && taps > 1)

@@ -101,7 +101,8 @@ def _signatures(lib):
         "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_int, c_void_p],
-        "mllm_norm_scale_add": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_void_p],
+        "mllm_norm_scale_add": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_float,
+                                c_float, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_latent_prepare": [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "mllm_headwise_linear": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int,
@@ -856,18 +857,41 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
 
 
 # --------------------------------------------------------------------------- joining a branch's result to the residual
-def norm_scale_add(y, weight, scale, x, eps: float) -> None:
-    """x += (y / sqrt(mean(y^2) + eps) * weight) * scale, row by row, all 32-bit; ``scale`` (a vector) may be None."""
-    _cuda("y", y, torch.float32, contiguous=False)
+def norm_scale_add(y, weight, scale, x, eps: float, *, pairs=None, pair_weights=None, top: int = 0, next_weight=None,
+                   next_eps: float = 0.0, next_offset: float = 0.0, next_out=None) -> None:
+    """x += (v / sqrt(mean(v^2) + eps) * weight) * scale, row by row, all 32-bit; ``scale`` (a vector) may be None.
+    v = y, plus sum_k pair_weights[t, k] * pairs[t * top + k] when ``pairs`` [T * top, D] is given (the chosen experts'
+    results of a routed feed-forward; y may then be None).  With ``next_weight`` the new x is also normed for the branch
+    that reads it next: next_out = x / sqrt(mean(x^2) + next_eps) * (next_weight + next_offset), float32 or bfloat16."""
     _cuda("x", x, torch.float32, contiguous=False)
     _cuda("weight", weight, torch.float32)
     if scale is not None:
         _cuda("scale", scale, torch.float32)
     R, D = x.shape
-    if tuple(y.shape) != (R, D) or weight.numel() != D or (scale is not None and scale.numel() != D):
-        raise KernelError(f"norm_scale_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {weight.numel()}")
-    _call("mllm_norm_scale_add", y.data_ptr(), _rows("y", y), weight.data_ptr(),
-          scale.data_ptr() if scale is not None else None, x.data_ptr(), _rows("x", x), R, D, float(eps), _stream())
+    if weight.numel() != D or (scale is not None and scale.numel() != D):
+        raise KernelError(f"norm_scale_add: x {tuple(x.shape)}, weight {weight.numel()}")
+    if y is not None:
+        _cuda("y", y, torch.float32, contiguous=False)
+        if tuple(y.shape) != (R, D):
+            raise KernelError(f"norm_scale_add: y {tuple(y.shape)}, x {tuple(x.shape)}")
+    if pairs is not None:
+        _cuda("pairs", pairs, torch.float32)
+        _cuda("pair_weights", pair_weights, torch.float32)
+        if tuple(pairs.shape) != (R * top, D) or pair_weights.numel() != R * top:
+            raise KernelError("norm_scale_add: pairs do not fit")
+    elif y is None:
+        raise KernelError("norm_scale_add: nothing to add")
+    if next_weight is not None:
+        _cuda("next_weight", next_weight, torch.float32)
+        _cuda("next_out", next_out, contiguous=False)
+        if next_weight.numel() != D or tuple(next_out.shape) != (R, D):
+            raise KernelError("norm_scale_add: the next norm does not fit")
+    _call("mllm_norm_scale_add", y.data_ptr() if y is not None else None, _rows("y", y) if y is not None else 0,
+          pairs.data_ptr() if pairs is not None else None, pair_weights.data_ptr() if pairs is not None else None, int(top),
+          weight.data_ptr(), scale.data_ptr() if scale is not None else None, x.data_ptr(), _rows("x", x),
+          next_weight.data_ptr() if next_weight is not None else None, float(next_offset), float(next_eps),
+          next_out.data_ptr() if next_weight is not None else None, _rows("next_out", next_out) if next_weight is not None else 0,
+          R, D, float(eps), _dt(next_out) if next_weight is not None else F32, _stream())
 
 
 # --------------------------------------------------------------------------- attention over a cache of latents
@@ -1000,9 +1024,9 @@ def ssd_conv(proj, off: int, weight, bias, state, conv_off: int, ctx, out, *, wr
     _call("mllm_ssd_conv", proj.data_ptr(), _rows("proj", proj), int(off), weight.data_ptr(), bias.data_ptr(), state.data_ptr(),
           state.stride(0), int(conv_off), ctx.token_seq.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(),
           out.data_ptr(), T, ctx.S, C, taps, int(write_state), _dt(proj), _stream())
-    if write_state and taps > 1:
+    if write_state and taps > 1 and T != ctx.S:
         global launches
-        launches += 1
+        launches += 1       # the state's update (steps of single tokens do both in one launch)
 
 
 def ssd_scan(xbc, proj, dt_off: int, dt_bias, A_log, D, state, ctx, y, *, heads: int, vdim: int, state_rows: int, groups: int,
@@ -1048,6 +1072,7 @@ def gated_group_norm(y, z, weight, out, groups: int, eps: float) -> None:
 
 # --------------------------------------------------------------------------- routed feed-forward
 MOE_MAX_EXPERTS = 512
+_moe_few_tokens = None
 
 
 def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int = 1, keep: int = 1) -> None:
@@ -1067,8 +1092,11 @@ def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int 
         raise KernelError("moe_route: shapes do not fit")
     _call("mllm_moe_route", h.data_ptr(), _rows("h", h), router.data_ptr(), T, D, E, int(top), int(groups), int(keep),
           idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), _dt(h), _stream())
-    global launches
-    launches += 1           # the sort
+    global launches, _moe_few_tokens
+    if _moe_few_tokens is None:
+        _moe_few_tokens = int(library().mllm_moe_few_tokens())
+    if T > _moe_few_tokens:
+        launches += 1       # the ordering is a launch of its own
 
 
 def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool) -> None:

@@ -72,16 +72,26 @@ def _branch(part, y, *args):
 
 def sandwich(layer, x, ctx, cache):
     """x <- join(x, branch(norm(x))) for the mixer and then for the feed-forward: the branch writes a 32-bit buffer of
-    its own, and the layer's join (``LayerSpec.mixer_join`` / ``ff_join``) brings it into the residual stream."""
+    its own, and the layer's join (``LayerSpec.mixer_join`` / ``ff_join``) brings it into the residual stream.  Where the
+    parts allow it, the mixer's join also norms the new x for the feed-forward (one kernel), and a routed feed-forward
+    leaves the weighted sum over a token's experts to its join (``forward_pairs``)."""
     import torch
+    from .norm import RMSNorm
     if layer.mixer_join is None or (layer.ff is not None and layer.ff_join is None):
         raise RuntimeError("sandwich arrangement: the layer has no join for a branch")
     y = ctx.ws.buf("branch_out", x.shape[0], x.shape[1], torch.float32)
     _branch(layer.mixer, y, _norm(layer.mixer_norm, layer.mixer, x, ctx), ctx, cache)
-    layer.mixer_join.forward(y, x, ctx)
+    fuse = layer.ff is not None and isinstance(layer.ff_norm, RMSNorm) and getattr(layer.mixer_join, "norms_next", False)
+    h = layer.mixer_join.forward(y, x, ctx, then_norm=layer.ff_norm) if fuse else layer.mixer_join.forward(y, x, ctx)
     if layer.ff is not None:
-        _branch(layer.ff, y, _norm(layer.ff_norm, layer.ff, x, ctx), ctx)
-        layer.ff_join.forward(y, x, ctx)
+        if not fuse:
+            h = _norm(layer.ff_norm, layer.ff, x, ctx)
+        if hasattr(layer.ff, "forward_pairs") and getattr(layer.ff_join, "takes_pairs", False):
+            shared, pairs = layer.ff.forward_pairs(h, ctx, y)
+            layer.ff_join.forward(y if shared else None, x, ctx, pairs=pairs)
+        else:
+            _branch(layer.ff, y, h, ctx)
+            layer.ff_join.forward(y, x, ctx)
     return x
 
 

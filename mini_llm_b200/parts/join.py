@@ -9,6 +9,9 @@ from .base import Join, ParamSpec, register_part
 
 
 class NormScaleJoin(Join):
+    norms_next = True       # forward(..., then_norm=) also norms the new x for the next branch
+    takes_pairs = True      # forward(..., pairs=) takes the weighted sum over a routed feed-forward's choices itself
+
     def __init__(self, hidden_size: int, eps: float, scaled: bool = True):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
@@ -21,8 +24,21 @@ class NormScaleJoin(Join):
             p["scale"] = ParamSpec((self.hidden_size,), "vector")
         return p
 
-    def forward(self, y, x, ctx):
-        self.rt.ops.norm_scale_add(y, self.weight, self.scale, x, self.eps)
+    def forward(self, y, x, ctx, pairs=None, then_norm=None):
+        """x += n(y [+ the weighted pairs], w) * s.  ``pairs``: (results [T * top, D], weights [T, top], top) of a routed
+        feed-forward whose weighted sum has not been taken yet (y may then be None).  ``then_norm``: an RMS norm that the
+        next branch applies to the new x; its result comes back (one kernel does both), else None."""
+        ops = self.rt.ops
+        kw = {}
+        if pairs is not None:
+            kw.update(pairs=pairs[0], pair_weights=pairs[1], top=pairs[2])
+        h = None
+        if then_norm is not None:
+            h = ctx.ws.buf("norm_out", x.shape[0], self.hidden_size, self.rt.act_dtype)
+            kw.update(next_weight=then_norm.weight, next_eps=then_norm.eps, next_offset=1.0 if then_norm.unit_offset else 0.0,
+                      next_out=h)
+        ops.norm_scale_add(y, self.weight, self.scale, x, self.eps, **kw)
+        return h
 
 
 register_part("join", "norm_scale", NormScaleJoin)

@@ -67,30 +67,50 @@ class MoEFeedForward(FeedForward):
             self.shared_first = torch.cat([params["shared.gate"], params["shared.up"]], 0).contiguous()
             self.shared_down = params["shared.down"]
 
-    def forward(self, h, ctx, out_accum, accumulate: bool = True):
+    def _experts(self, h, ctx):
+        """Route, order, and run the chosen experts: (results per (token, choice) [T * top, D] 32-bit, weights [T, top])."""
         import torch
         ops = self.rt.ops
-        if isinstance(h, ops.NormedInput):
-            h = h.materialize()
         T, top, E = h.shape[0], self.top, self.num_experts
-        act = self.rt.act_dtype
         idx = ctx.ws.buf("moe_idx", T, top, torch.int32)
         wts = ctx.ws.buf("moe_weights", T, top, torch.float32)
         order = ctx.ws.buf("moe_order", T, top, torch.int32)
         offsets = ctx.ws.buf("moe_offsets", 1, E + 1, torch.int32)
         ops.moe_route(h, self.router, idx, wts, offsets, order, top=top, groups=self.groups, keep=self.keep)
-        mid = ctx.ws.buf("moe_mid", T * top, self.expert_size, act)
+        mid = ctx.ws.buf("moe_mid", T * top, self.expert_size, self.rt.act_dtype)
         ops.moe_grouped(h, self.w_first, mid, offsets, order, top=top, first=True)
         pair_out = ctx.ws.buf("moe_pair_out", T * top, self.hidden_size, torch.float32)
         ops.moe_grouped(mid, self.w_second, pair_out, offsets, order, top=top, first=False)
+        return pair_out, wts
+
+    def _shared(self, h, ctx, out, accumulate):
+        ops = self.rt.ops
+        T = h.shape[0]
+        gu = ctx.ws.buf("ff_gate_up", T, 2 * self.shared_size, self.rt.act_dtype)
+        ops.linear(h, self.shared_first, None, out=gu)
+        smid = ctx.ws.buf("ff_mid", T, self.shared_size, self.rt.act_dtype)
+        ops.gated_act(gu, smid, self.activation)
+        ops.linear(smid, self.shared_down, None, out=out, accumulate=accumulate)
+
+    def forward_pairs(self, h, ctx, y):
+        """For a join that takes the weighted sum itself: the shared expert's result goes to y (if there is one), the
+        chosen experts' results stay apart.  Returns (whether y was written, (results, weights, top))."""
+        if isinstance(h, self.rt.ops.NormedInput):
+            h = h.materialize()
+        pair_out, wts = self._experts(h, ctx)
         if self.shared_size is not None:
-            gu = ctx.ws.buf("ff_gate_up", T, 2 * self.shared_size, act)
-            ops.linear(h, self.shared_first, None, out=gu)
-            smid = ctx.ws.buf("ff_mid", T, self.shared_size, act)
-            ops.gated_act(gu, smid, self.activation)
-            ops.linear(smid, self.shared_down, None, out=out_accum, accumulate=accumulate)
+            self._shared(h, ctx, y, False)
+        return self.shared_size is not None, (pair_out, wts, self.top)
+
+    def forward(self, h, ctx, out_accum, accumulate: bool = True):
+        ops = self.rt.ops
+        if isinstance(h, ops.NormedInput):
+            h = h.materialize()
+        pair_out, wts = self._experts(h, ctx)
+        if self.shared_size is not None:
+            self._shared(h, ctx, out_accum, accumulate)
             accumulate = True
-        ops.moe_combine(pair_out, wts, out_accum, top=top, accumulate=accumulate)
+        ops.moe_combine(pair_out, wts, out_accum, top=self.top, accumulate=accumulate)
 
 
 register_part("feed_forward", "moe", MoEFeedForward)

@@ -71,6 +71,30 @@ def test_norm_scale_add(ops, R, D, eps):
     assert abs(out[0, 0].item() - 1e-4 / math.sqrt(1e-8 + 1e-2)) < 1e-9
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,D,top,eps", [(5, 48, 2, 1e-5), (3, 1001, 1, 1e-3), (2, 4096, 3, 1e-6), (33, 20000, 2, 1e-5)])
+def test_join_takes_the_weighted_pairs_and_norms_for_the_next_branch(ops, out_dtype, R, D, top, eps):
+    """One kernel: the weighted sum over a token's experts (with or without a result to add it to), the norm and scale
+    of that sum, the residual sum, and the next branch's norm of the new stream (plain weights or weights around zero)."""
+    y, x0 = rnd(R, D, seed=1, scale=3.0), rnd(R, D, seed=2)
+    w, ls, nw = rnd(D, seed=3) + 1.0, rnd(D, seed=4, scale=0.5), rnd(D, seed=5, scale=0.3) + 0.2
+    pairs, pw = rnd(R * top, D, seed=6, scale=2.0), torch.rand(R, top, generator=torch.Generator().manual_seed(7)).to(DEV)
+    mix = (pw.double().cpu()[:, :, None] * pairs.double().cpu().view(R, top, D)).sum(1)
+    for with_y in (True, False):
+        for offset in (0.0, 1.0):
+            x = x0.clone()
+            h = torch.zeros(R, D, device=DEV, dtype=out_dtype)
+            ops.norm_scale_add(y if with_y else None, w, ls, x, eps, pairs=pairs, pair_weights=pw, top=top, next_weight=nw,
+                               next_eps=2 * eps, next_offset=offset, next_out=h)
+            v = mix + (y.double().cpu() if with_y else 0.0)
+            want = x0.double().cpu() + P.rms_norm(v, w.double().cpu(), eps) * ls.double().cpu()
+            assert _rel(x, want) < 2e-6
+            assert _rel(h, P.rms_norm(want, nw.double().cpu() + offset, 2 * eps)) < (2e-6 if out_dtype == torch.float32 else 1e-2)
+    x = x0.clone()
+    ops.norm_scale_add(None, w, None, x, eps, pairs=pairs, pair_weights=pw, top=top)
+    assert _rel(x, x0.double().cpu() + P.rms_norm(mix, w.double().cpu(), eps)) < 2e-6
+
+
 # ------------------------------------------------------------------------------------------------ latent rows, rotation
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,dn,dr,R,dims,scaling", [(3, 16, 8, 40, 8, dict(factor=4.0, original=32, fast=8.0, slow=1.0)),
