@@ -130,6 +130,42 @@ headwise_linear_kernel(const TI* in, long long ld_in, int in_head, const TW* __r
     }
 }
 
+// The same products for few tokens (decode steps): grid (tokens, heads, column blocks of 64), 8 warps.  The token's K
+// inputs of the head are staged in shared memory as 32-bit; a warp owns 8 columns, its lanes split K (the 8 weight rows'
+// loads in flight together), the sums meet by a butterfly.
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+headwise_rows_kernel(const TI* in, long long ld_in, int in_head, const TW* __restrict__ W, TO* out, long long ld_out,
+                     int out_head, const TO* gate, long long ld_gate, int N, int K) {
+    extern __shared__ float hx[];                                // [K]
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const TI* x = in + (size_t)t * ld_in + (size_t)h * in_head;
+    for (int k = threadIdx.x; k < K; k += 256) hx[k] = to_f32(x[k]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.z * 64 + warp * 8;
+    if (n0 >= N) return;
+    const TW* Wh = W + (size_t)h * N * K;
+    float acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float xv = hx[k];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = fmaf(xv, to_f32(Wh[(size_t)min(n0 + u, N - 1) * K + k]), acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        float v = warp_sum(acc[u]);
+        const int n = n0 + u;
+        if (lane == 0 && n < N) {
+            if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ld_gate + (size_t)h * N + n])));
+            out[(size_t)t * ld_out + (size_t)h * out_head + n] = from_f32<TO>(v);
+        }
+    }
+}
+
 // grid (splits, tokens, head blocks); dynamic shared memory: HB * dkp floats of queries, then two chunks of 32 key rows
 // of `kw` 32-bit words each (kw = a row's words + 4: rows stay 16-byte aligned for cp.async and 128-bit reads, and eight
 // lanes reading 16 bytes of eight consecutive rows touch all 32 banks).  A CTA walks the keys [split * span, ...) of its
@@ -553,6 +589,24 @@ MLLM_EXPORT int mllm_headwise_linear(const void* in, long long ld_in, int in_hea
     const dim3 grid((Tn + 31) / 32, (N + 63) / 64, H), block(256);
     if (grid.y > 65535 || grid.z > 65535) return mllm_fail(1, "headwise_linear: grid too large");
     if (mode == 0 && gate) return mllm_fail(1, "headwise_linear: a gate needs mode 1");
+    if (Tn <= 16 && (size_t)K * 4 <= 48 * 1024 && H <= 65535) {                 // few tokens: every (token, head) streams its weights
+        const dim3 rg(Tn, H, (N + 63) / 64);
+        const size_t smem = (size_t)K * 4;
+        if (dtype == MLLM_F32)
+            MLLM_CUDA(mllm_launch(headwise_rows_kernel<float, float, float>, rg, block, smem, stream, true, (const float*)in, ld_in,
+                                  in_head, (const float*)W, (float*)out, ld_out, out_head, (const float*)gate, ld_gate, N, K));
+        else if (dtype == MLLM_BF16 && mode == 0)
+            MLLM_CUDA(mllm_launch(headwise_rows_kernel<__nv_bfloat16, __nv_bfloat16, float>, rg, block, smem, stream, true,
+                                  (const __nv_bfloat16*)in, ld_in, in_head, (const __nv_bfloat16*)W, (float*)out, ld_out, out_head,
+                                  (const float*)nullptr, ld_gate, N, K));
+        else if (dtype == MLLM_BF16)
+            MLLM_CUDA(mllm_launch(headwise_rows_kernel<float, __nv_bfloat16, __nv_bfloat16>, rg, block, smem, stream, true,
+                                  (const float*)in, ld_in, in_head, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ld_out, out_head,
+                                  (const __nv_bfloat16*)gate, ld_gate, N, K));
+        else
+            return mllm_fail(1, "headwise_linear: unknown dtype code %d", dtype);
+        return 0;
+    }
     if (dtype == MLLM_F32) {
         MLLM_CUDA(mllm_launch(headwise_linear_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)in, ld_in,
                               in_head, (const float*)W, (float*)out, ld_out, out_head, (const float*)gate, ld_gate, Tn, N, K));

@@ -24,12 +24,49 @@ constexpr int MOE_FEW_PAIRS = 32;     // up to this many (token, choice) pairs e
 template <typename T>
 __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr, float* s, int D, int E, int top, int n_groups,
                                             int keep, int* idx, float* wout, int lane) {
-    for (int e = 0; e < E; ++e) {
-        const T* w = Wr + (size_t)e * D;
-        float a = 0.f;
-        for (int d = lane; d < D; d += 32) a = fmaf(to_f32(x[d]), to_f32(w[d]), a);
-        a = warp_sum(a);
-        if (lane == 0) s[e] = a;
+    constexpr int V = 16 / sizeof(T);                           // elements per 16-byte load
+    const bool vec = D % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)Wr % 16 == 0;
+    for (int e0 = 0; e0 < E; e0 += 4) {                         // four experts at a time: their loads are in flight together
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        const T* w0 = Wr + (size_t)e0 * D;
+        const T* w1 = Wr + (size_t)min(e0 + 1, E - 1) * D;
+        const T* w2 = Wr + (size_t)min(e0 + 2, E - 1) * D;
+        const T* w3 = Wr + (size_t)min(e0 + 3, E - 1) * D;
+        if (vec) {
+#pragma unroll 2
+            for (int d = lane * V; d < D; d += 32 * V) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(x + d);
+                const uint4 v0 = *reinterpret_cast<const uint4*>(w0 + d), v1 = *reinterpret_cast<const uint4*>(w1 + d);
+                const uint4 v2 = *reinterpret_cast<const uint4*>(w2 + d), v3 = *reinterpret_cast<const uint4*>(w3 + d);
+                const T* px = reinterpret_cast<const T*>(&xv);
+                const T* p0 = reinterpret_cast<const T*>(&v0);
+                const T* p1 = reinterpret_cast<const T*>(&v1);
+                const T* p2 = reinterpret_cast<const T*>(&v2);
+                const T* p3 = reinterpret_cast<const T*>(&v3);
+#pragma unroll
+                for (int c = 0; c < V; ++c) {
+                    const float xf = to_f32(px[c]);
+                    a[0] = fmaf(xf, to_f32(p0[c]), a[0]);
+                    a[1] = fmaf(xf, to_f32(p1[c]), a[1]);
+                    a[2] = fmaf(xf, to_f32(p2[c]), a[2]);
+                    a[3] = fmaf(xf, to_f32(p3[c]), a[3]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int d = lane; d < D; d += 32) {
+                const float xv = to_f32(x[d]);
+                a[0] = fmaf(xv, to_f32(w0[d]), a[0]);
+                a[1] = fmaf(xv, to_f32(w1[d]), a[1]);
+                a[2] = fmaf(xv, to_f32(w2[d]), a[2]);
+                a[3] = fmaf(xv, to_f32(w3[d]), a[3]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float v = warp_sum(a[u]);
+            if (lane == 0 && e0 + u < E) s[e0 + u] = v;
+        }
     }
     __syncwarp();
     float mx = -INFINITY;
