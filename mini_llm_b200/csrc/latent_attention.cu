@@ -9,6 +9,8 @@
 //                    and columns R.. of qa.
 //   headwise_linear  out[t][h][n] = sum_k in[t][h][k] W[h][n][k] (optionally times sigmoid(gate[t][h][n])):
 //                    the absorbed query (W = W_uk^T per head) and the head outputs (W = W_uv per head, with the gate).
+//                    Three kernels: CUDA-core tiles (32-bit weights, odd sizes), tensor-core tiles (bfloat16 weights,
+//                    more than 16 tokens), and for up to 16 tokens a CTA per (token, head) that streams its weights.
 //   latent_attention one CTA per (split of `span` keys, token, block of 8 heads): key rows are staged once for all the
 //                    heads of the block in chunks of 32 that start at multiples of 32 from position 0; a warp is a
 //                    head, its lanes are the 32 keys for the scores and 64 latent columns at a time for the weighted
@@ -555,6 +557,83 @@ int launch_mma(const float* qa, const void* pages, int row, const int* bt, int b
     return launch_mma_q<NO, CW, 0>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
 }
 
+// The per-head products of many tokens on tensor cores (bfloat16 weights): 64 tokens x 64 columns per CTA and head, K in
+// steps of 64.  MODE 0: inputs in bfloat16 (cp.async), result 32-bit.  MODE 1: inputs 32-bit, taken as hi + lo bfloat16
+// terms so that they keep about 16 bits; result bfloat16, optionally times sigmoid(gate).
+template <int MODE>
+__global__ void __launch_bounds__(128)
+headwise_mma_kernel(const void* in_, long long ld_in, int in_head, const __nv_bfloat16* __restrict__ W, void* out_,
+                    long long ld_out, int out_head, const __nv_bfloat16* gate, long long ld_gate, int Tn, int N, int K) {
+    using bf = __nv_bfloat16;
+    constexpr int LD = 72;
+    __shared__ __align__(16) bf As[64 * LD];
+    __shared__ __align__(16) bf Al[MODE ? 64 * LD : 8];
+    __shared__ __align__(16) bf Ws[64 * LD];
+    pdl_wait();
+    const int h = blockIdx.z, t0 = blockIdx.x * 64, n0 = blockIdx.y * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+    for (int k0 = 0; k0 < K; k0 += 64) {
+        __syncthreads();                                         // the tiles of the step before have been used
+        for (int i = tid; i < 64 * 8; i += 128) {
+            const int r = i >> 3, pc = i & 7, k = k0 + pc * 8;
+            const bool ok = n0 + r < N && k < K;
+            cp_async16(Ws + r * LD + pc * 8, ok ? W + ((size_t)h * N + n0 + r) * K + k : W, ok);
+            if (MODE == 0) {
+                const bf* in = reinterpret_cast<const bf*>(in_);
+                const bool oka = t0 + r < Tn && k < K;
+                cp_async16(As + r * LD + pc * 8, oka ? in + (size_t)(t0 + r) * ld_in + (size_t)h * in_head + k : in, oka);
+            }
+        }
+        if (MODE == 1) {
+            const float* in = reinterpret_cast<const float*>(in_);
+            for (int i = tid; i < 64 * 32; i += 128) {
+                const int r = i >> 5, k = k0 + 2 * (i & 31);
+                float2 v = make_float2(0.f, 0.f);
+                if (t0 + r < Tn && k < K) v = *reinterpret_cast<const float2*>(in + (size_t)(t0 + r) * ld_in + (size_t)h * in_head + k);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+                *reinterpret_cast<__nv_bfloat162*>(As + r * LD + 2 * (i & 31)) = hi;
+                *reinterpret_cast<__nv_bfloat162*>(Al + r * LD + 2 * (i & 31)) = __floats2bfloat162_rn(v.x - __low2float(hi), v.y - __high2float(hi));
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 64; kk += 16) {
+            uint32_t af[4], al[4];
+            ldsm_x4(af, As + (warp * 16 + (lane & 15)) * LD + kk + (lane >> 4) * 8);
+            if (MODE == 1) ldsm_x4(al, Al + (warp * 16 + (lane & 15)) * LD + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                uint32_t b[2];
+                ldsm_x2(b, Ws + (n * 8 + (lane & 7)) * LD + kk + ((lane >> 3) & 1) * 8);
+                mma_bf16(acc[n], af, b);
+                if (MODE == 1) mma_bf16(acc[n], al, b);
+            }
+        }
+    }
+    const int r0 = warp * 16 + (lane >> 2);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int t = t0 + r0 + (c >> 1) * 8, col = n0 + n * 8 + 2 * (lane & 3) + (c & 1);
+            if (t < Tn && col < N) {
+                float v = acc[n][c];
+                if (MODE == 0) {
+                    reinterpret_cast<float*>(out_)[(size_t)t * ld_out + (size_t)h * out_head + col] = v;
+                } else {
+                    if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ld_gate + (size_t)h * N + col])));
+                    reinterpret_cast<bf*>(out_)[(size_t)t * ld_out + (size_t)h * out_head + col] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // proj [T, ...] in `dtype` with row stride ld: queries at column q_off (H heads of dn + dr), the down-projection at
@@ -606,6 +685,19 @@ MLLM_EXPORT int mllm_headwise_linear(const void* in, long long ld_in, int in_hea
         else
             return mllm_fail(1, "headwise_linear: unknown dtype code %d", dtype);
         return 0;
+    }
+    if (dtype == MLLM_BF16 && K % 8 == 0 && (uintptr_t)W % 16 == 0) {            // many tokens, bfloat16: tensor cores
+        const dim3 mg((Tn + 63) / 64, (N + 63) / 64, H);
+        if (mode == 0 && ld_in % 8 == 0 && in_head % 8 == 0 && (uintptr_t)in % 16 == 0) {
+            MLLM_CUDA(mllm_launch(headwise_mma_kernel<0>, mg, dim3(128), 0, stream, true, in, ld_in, in_head, (const __nv_bfloat16*)W, out,
+                                  ld_out, out_head, (const __nv_bfloat16*)nullptr, ld_gate, Tn, N, K));
+            return 0;
+        }
+        if (mode == 1 && ld_in % 2 == 0 && in_head % 2 == 0 && (uintptr_t)in % 8 == 0) {
+            MLLM_CUDA(mllm_launch(headwise_mma_kernel<1>, mg, dim3(128), 0, stream, true, in, ld_in, in_head, (const __nv_bfloat16*)W, out,
+                                  ld_out, out_head, (const __nv_bfloat16*)gate, ld_gate, Tn, N, K));
+            return 0;
+        }
     }
     if (dtype == MLLM_F32) {
         MLLM_CUDA(mllm_launch(headwise_linear_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)in, ld_in,

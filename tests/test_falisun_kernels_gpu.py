@@ -154,6 +154,30 @@ def test_headwise_linear(ops, dtype, T, H, N, K):
     assert _rel(out2.view(T, H, N), want2) < _tol(dtype)
 
 
+@pytest.mark.parametrize("T,H,N,K", [(17, 3, 40, 16), (200, 2, 136, 72), (64, 5, 8, 64), (130, 1, 65, 8)])
+def test_headwise_linear_on_tensor_cores(ops, T, H, N, K):
+    """More than 16 tokens, bfloat16 weights, 16-byte aligned rows: both directions against float64."""
+    x = rnd(T, H * (K + 8) + 16, seed=1, dtype=torch.bfloat16)
+    W = rnd(H, N, K, seed=2, scale=K ** -0.5, dtype=torch.bfloat16)
+    out = torch.zeros(T, H * (N + 3), device=DEV)
+    ops.headwise_linear(x[:, :H * (K + 8)], K + 8, W, out, N + 3)
+    xs = x.double().cpu()[:, :H * (K + 8)].view(T, H, K + 8)[..., :K]
+    want = torch.einsum("thk,hnk->thn", xs, W.double().cpu())
+    assert _rel(out.view(T, H, N + 3)[..., :N], want) < 2e-5 and torch.all(out.view(T, H, N + 3)[..., N:] == 0)
+    y = rnd(T, H * K, seed=3)
+    g = rnd(T, H * N + 8, seed=4, dtype=torch.bfloat16)
+    out2 = torch.zeros(T, H * N, dtype=torch.bfloat16, device=DEV)
+    ops.headwise_linear(y, K, W, out2, N, gate=g[:, 8:])
+    want2 = torch.einsum("thk,hnk->thn", y.double().cpu().view(T, H, K), W.double().cpu()) \
+        * torch.sigmoid(g.double().cpu()[:, 8:].view(T, H, N))
+    assert _rel(out2.view(T, H, N), want2) < 1.2e-2
+    # the 32-bit inputs keep about 16 bits: against a 32-bit result of the same product the difference is far below bfloat16's
+    out3 = torch.zeros(T, H * N, device=DEV)
+    ops.headwise_linear(y, K, W.float(), out3, N)
+    want3 = torch.einsum("thk,hnk->thn", y.double().cpu().view(T, H, K), W.double().cpu())
+    assert _rel(out3.view(T, H, N), want3) < 2e-5
+
+
 def _latent_case(dtype, seqs, H, R, dr, page, seed, sharp=None):
     """Cache rows in shuffled pages, queries for the new tokens.  ``sharp``: {request: [positions]}: the rows there answer
     a direction that all of the request's queries share with a score that stands out, so a row that is dropped, wrongly
