@@ -355,6 +355,43 @@ def test_sizes_that_happen_to_be_one_or_equal(tmp_path):
         close(np.concatenate(rows), want, dtype, "ones")
 
 
+@pytest.mark.parametrize("kind", ["attention_only", "mamba_only"])
+def test_models_of_one_kind_of_layer(tmp_path, kind):
+    """Only pages and no state, or only states and no pages: whole, in portions and token by token, two requests."""
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+    if kind == "attention_only":
+        layers = [layer("latent_attention", latent(2, 8, 8, 8, 16, 0.4, base=50.0), moe(4, 2, 16, shared=8)),
+                  layer("latent_attention", latent(3, 16, 8, 8, 16, 0.3, base=50.0, kv_from=0), None),
+                  layer("latent_attention", latent(2, 8, 8, 8, 16, 0.4, base=50.0), None)]
+    else:
+        layers = [layer("mamba2", mamba(2, 16, 16, 1, 4, 1), None), layer("mamba2", mamba(4, 8, 24, 2, 2, 2), moe(4, 2, 16, shared=8))]
+    cfg = config(48, 61, 1e-5, layers)
+    tensors = make_tensors(cfg, 6)
+    folder = write_model(str(tmp_path / kind), cfg, tensors, torch.bfloat16)
+    ids = {k: random_ids(n, cfg["vocab"], 30 + n) for k, n in (("a", 70), ("b", 41))}
+    want = {k: oracle(tensors, cfg, v, "float32") for k, v in ids.items()}
+    r = ModelRunner(folder, EngineConfig(dtype="float32", page_size=8, num_pages=20, max_num_seqs=2))
+    assert (len(r.cache.groups) == 0) == (kind == "mamba_only") and (len(r.cache.states) == 0) == (kind == "attention_only")
+    for k in ids:
+        r.add_request(k)
+    got = {k: [] for k in ids}
+    out = r.step([StepEntry("a", ids["a"][:50], list(range(50))), StepEntry("b", ids["b"][:3], [0, 1, 2])]).cpu().numpy()
+    got["a"].append(out[:50]); got["b"].append(out[50:])
+    out = r.step([StepEntry("b", ids["b"][3:40], list(range(37))), StepEntry("a", [ids["a"][50]], [0])]).cpu().numpy()
+    got["b"].append(out[:37]); got["a"].append(out[37:])
+    for t in range(51, 70):
+        entries = [StepEntry("a", [ids["a"][t]], [0])] + ([StepEntry("b", [ids["b"][40]], [0])] if t == 51 else [])
+        out = r.step(entries).cpu().numpy()
+        got["a"].append(out[:1])
+        if t == 51:
+            got["b"].append(out[1:])
+    for k in ids:
+        close(np.concatenate(got[k]), want[k], "float32", f"{kind} {k}")
+        r.finish_request(k)
+    r.cache.check()
+
+
 def test_sizes_no_kernel_takes_are_refused_at_construction(tmp_path):
     from mini_llm_b200.config.base import ConfigError, EngineConfig
     from mini_llm_b200.engine.runner import ModelRunner
