@@ -354,13 +354,15 @@ int pick_attention(int R, const float* qa, const void* pages, int row, const int
 // The same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit accumulators) for a bfloat16 cache.
 // A CTA takes one tile of up to 64 new tokens of one request and one head; warp (rg, cs) owns the 16 query rows rg*16..
 // and the latent columns cs*NO*8.. of the result (CW column parts: a warp's output sums stay in registers also for
-// latents of 512).  Key tile j covers the positions [32j, 32j + 32): its rows come into shared memory by cp.async as
+// latents of 512; the two warps of a row group then split the tile's keys for the scores and share the weights).  Key tile j covers the positions [32j, 32j + 32): its rows come into shared memory by cp.async as
 // they lie in the pages (rows nobody sees are zero-filled), the next tile's while the current one is used, and serve
 // twice: as keys (all R + dr columns) and, read transposed, as values (the first R columns).  The absorbed queries are
 // taken as hi + lo, two bfloat16 terms (hi alone where shared memory cannot hold both: rows beyond 520 columns), so the
 // scores keep about 16 bits of them; scores, mask and the online softmax are 32-bit (scores in units of ln 2, ex2.approx); the
 // weights enter the second product as p = hi + lo, two bfloat16 terms, so they keep about 16 bits; output sums 32-bit.
 constexpr int MQ = 64, MK = 32;
+constexpr int PLD = MK + 8;                                      // row stride of the shared weights
+constexpr int PAIR_BYTES = 4 * 2 * 16 * PLD * 2 + 4 * 2 * 16 * 4;   // shared weights and maxima of the four row groups
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
@@ -394,6 +396,9 @@ __device__ __forceinline__ float ex2(float x) {                   // 2^x in one 
     return y;
 }
 
+// barrier of the two warps (64 threads) of row group rg
+__device__ __forceinline__ void pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
+
 template <int NO, int CW, int QL>
 __global__ void __launch_bounds__(128 * CW)
 latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const int* __restrict__ block_table, int bt_stride,
@@ -405,6 +410,8 @@ latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const in
     bf* Qs = reinterpret_cast<bf*>(smraw);                       // [MQ][dk + 8], and with QL once more for the low terms
     bf* Ql = Qs + MQ * srow;
     bf* Ks = Qs + (QL ? 2 : 1) * MQ * srow;                      // [2][MK][dk + 8]
+    bf* Ps = Ks + 2 * MK * srow;                                 // with two column parts: [4 row groups][hi, lo][16][PLD] weights
+    float* Mx = reinterpret_cast<float*>(Ps + 4 * 2 * 16 * PLD); // and [4][2][16] row maxima (row sums at the end)
     pdl_wait();
     const int tile = blockIdx.y, h = blockIdx.x;
     const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
@@ -449,27 +456,31 @@ latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const in
         if (j < j_last) stage(j + 1, buf ^ 1);
         const bf* kt = Ks + buf * MK * srow;
         if (j * MK > pos0 + rg * 16 + 15 || rg * 16 >= rows) continue;      // nothing of the tile is seen by this warp's rows
-        float s[4][4];
+        // With two column parts a row group's two warps share the scores: each multiplies its 16 keys of the tile, the
+        // maxima and the weights (hi and lo terms) meet in shared memory on a barrier of the pair's 64 threads.
+        constexpr int NS = CW == 2 ? 2 : 4;                      // score tiles of 8 keys per warp
+        const int nb = CW == 2 ? cs * 2 : 0;                     // the first of them
+        float s[NS][4];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        for (int n = 0; n < NS; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
         for (int k0 = 0; k0 < dk; k0 += 16) {
             uint32_t af[4], al[4];
             ldsm_x4(af, Qs + (rg * 16 + (lane & 15)) * srow + k0 + (lane >> 4) * 8);
             if (QL) ldsm_x4(al, Ql + (rg * 16 + (lane & 15)) * srow + k0 + (lane >> 4) * 8);
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < NS; ++n) {
                 uint32_t bfr[2];
-                ldsm_x2(bfr, kt + (n * 8 + (lane & 7)) * srow + k0 + ((lane >> 3) & 1) * 8);
+                ldsm_x2(bfr, kt + ((nb + n) * 8 + (lane & 7)) * srow + k0 + ((lane >> 3) & 1) * 8);
                 mma_bf16(s[n], af, bfr);
                 if (QL) mma_bf16(s[n], al, bfr);
             }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
+        for (int n = 0; n < NS; ++n) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int kp = j * MK + n * 8 + 2 * (lane & 3) + (e & 1);
+                const int kp = j * MK + (nb + n) * 8 + 2 * (lane & 3) + (e & 1);
                 const int qp = (e < 2) ? qp0 : qp1;
                 const float sc = (kp <= qp && qp <= pos_max) ? s[n][e] * sf : -INFINITY;
                 s[n][e] = sc;
@@ -480,23 +491,49 @@ latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const in
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if constexpr (CW == 2) {
+            float* mine = Mx + (rg * 2 + cs) * 16;
+            if ((lane & 3) == 0) { mine[lane >> 2] = mx0; mine[8 + (lane >> 2)] = mx1; }
+            pair_sync(rg);
+            const float* other = Mx + (rg * 2 + (cs ^ 1)) * 16;
+            mx0 = fmaxf(mx0, other[lane >> 2]);
+            mx1 = fmaxf(mx1, other[8 + (lane >> 2)]);
+        }
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
         const float al0 = ex2(m0 - mu0), al1 = ex2(m1 - mu1);
         m0 = mn0; m1 = mn1;
         float rs0 = 0.f, rs1 = 0.f;
         uint32_t phi[2][4], plo[2][4];                           // A fragments of p for the two 16-key steps
+        bf* ph = Ps + (rg * 2) * 16 * PLD;                       // the row group's weights: hi terms, then lo terms
+        bf* pl = ph + 16 * PLD;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
+        for (int n = 0; n < NS; ++n) {
             const float p0 = ex2(s[n][0] - mu0), p1 = ex2(s[n][1] - mu0), p2 = ex2(s[n][2] - mu1), p3 = ex2(s[n][3] - mu1);
             rs0 += p0 + p1;
             rs1 += p2 + p3;
             const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
-            const int kk = n >> 1, half = (n & 1) * 2;
-            phi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
-            phi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
-            plo[kk][half] = pack_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
-            plo[kk][half + 1] = pack_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
+            if constexpr (CW == 2) {
+                const int col = (nb + n) * 8 + 2 * (lane & 3), ra = (lane >> 2) * PLD + col, rb = ((lane >> 2) + 8) * PLD + col;
+                *reinterpret_cast<__nv_bfloat162*>(ph + ra) = h01;
+                *reinterpret_cast<__nv_bfloat162*>(ph + rb) = h23;
+                *reinterpret_cast<__nv_bfloat162*>(pl + ra) = __floats2bfloat162_rn(p0 - __low2float(h01), p1 - __high2float(h01));
+                *reinterpret_cast<__nv_bfloat162*>(pl + rb) = __floats2bfloat162_rn(p2 - __low2float(h23), p3 - __high2float(h23));
+            } else {
+                const int kk = n >> 1, half = (n & 1) * 2;
+                phi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+                phi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                plo[kk][half] = pack_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
+                plo[kk][half + 1] = pack_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
+            }
+        }
+        if constexpr (CW == 2) {
+            pair_sync(rg);
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                ldsm_x4(phi[kk], ph + (lane & 15) * PLD + kk * 16 + (lane >> 4) * 8);
+                ldsm_x4(plo[kk], pl + (lane & 15) * PLD + kk * 16 + (lane >> 4) * 8);
+            }
         }
         l0 = l0 * al0 + rs0;                                     // per-thread part of the row sums; the quad meets at the end
         l1 = l1 * al1 + rs1;
@@ -522,6 +559,14 @@ latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const in
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if constexpr (CW == 2) {                                     // each warp of a pair has summed the weights of its own keys
+        float* mine = Mx + (rg * 2 + cs) * 16;
+        if ((lane & 3) == 0) { mine[lane >> 2] = l0; mine[8 + (lane >> 2)] = l1; }
+        pair_sync(rg);
+        const float* other = Mx + (rg * 2 + (cs ^ 1)) * 16;
+        l0 += other[lane >> 2];
+        l1 += other[8 + (lane >> 2)];
+    }
     const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
 #pragma unroll
     for (int i = 0; i < NO; ++i) {
@@ -538,7 +583,7 @@ latent_mma_kernel(const float* qa, const __nv_bfloat16* pages, int row, const in
 template <int NO, int CW, int QL>
 int launch_mma_q(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* tiles, int n_tiles,
                const int* positions, float* out, int H, int R, int dk, int ps, float scale, cudaStream_t stream) {
-    const size_t smem = (size_t)((QL ? 2 : 1) * MQ + 2 * MK) * (dk + 8) * 2;
+    const size_t smem = (size_t)((QL ? 2 : 1) * MQ + 2 * MK) * (dk + 8) * 2 + (CW == 2 ? PAIR_BYTES : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
         MLLM_CUDA(cudaFuncSetAttribute(latent_mma_kernel<NO, CW, QL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -552,7 +597,7 @@ int launch_mma_q(const float* qa, const void* pages, int row, const int* bt, int
 template <int NO, int CW>
 int launch_mma(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* tiles, int n_tiles,
                const int* positions, float* out, int H, int R, int dk, int ps, float scale, cudaStream_t stream) {
-    if ((size_t)(2 * MQ + 2 * MK) * (dk + 8) * 2 <= 200 * 1024)
+    if ((size_t)(2 * MQ + 2 * MK) * (dk + 8) * 2 + (CW == 2 ? PAIR_BYTES : 0) <= 200 * 1024)
         return launch_mma_q<NO, CW, 1>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
     return launch_mma_q<NO, CW, 0>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
 }
@@ -747,7 +792,7 @@ MLLM_EXPORT int mllm_latent_attention(const float* qa, const void* pages, int ro
 // 1 if the tensor-core kernel for prompt portions takes these sizes (a bfloat16 cache is the caller's to check).
 MLLM_EXPORT int mllm_latent_mma_ok(int R, int dk, int row) {
     return R > 0 && R % 8 == 0 && R <= MAX_R && dk % 16 == 0 && dk >= R && row >= dk && row % 8 == 0 &&
-           (size_t)(MQ + 2 * MK) * (dk + 8) * 2 <= 200 * 1024;
+           (size_t)(MQ + 2 * MK) * (dk + 8) * 2 + PAIR_BYTES <= 200 * 1024;
 }
 
 // Prompt portions with a bfloat16 cache: tiles [n_tiles][3] = (request, first flat token, rows <= 64).
@@ -762,5 +807,6 @@ MLLM_EXPORT int mllm_latent_attention_mma(const float* qa, const void* pages, in
     if (R <= 64) return launch_mma<8, 1>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
     if (R <= 128) return launch_mma<16, 1>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
     if (R <= 256) return launch_mma<16, 2>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
+    if (R <= 384) return launch_mma<24, 2>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
     return launch_mma<32, 2>(qa, pages, row, block_table, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
 }
