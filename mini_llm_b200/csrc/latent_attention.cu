@@ -23,6 +23,7 @@
 namespace {
 
 constexpr int HB = 8;           // heads (warps) per CTA
+constexpr int MAX_SMEM = 227 * 1024;    // dynamic shared memory a CTA can have on this GPU
 constexpr int MAX_R = 512;      // largest latent size
 constexpr int MAX_DK = 1024;    // largest R + dr
 
@@ -325,10 +326,10 @@ int launch_attention(const float* qa, const void* pages, int row, const int* bt,
     const size_t smem = (size_t)HB * dkp * 4 + (size_t)2 * 32 * kw * 4;
     static bool raised = false;                     // once per instantiation
     if (smem > 48 * 1024 && !raised) {
-        MLLM_CUDA(cudaFuncSetAttribute(latent_attention_kernel<T, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        MLLM_CUDA(cudaFuncSetAttribute(latent_attention_kernel<T, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM));
         raised = true;
     }
-    if (smem > 200 * 1024) return mllm_fail(1, "latent_attention: rows of %d need %zu bytes of shared memory", dk, smem);
+    if (smem > MAX_SMEM) return mllm_fail(1, "latent_attention: rows of %d need %zu bytes of shared memory", dk, smem);
     MLLM_CUDA(mllm_launch(latent_attention_kernel<T, NACC>, dim3(nsplit, Tn, (H + HB - 1) / HB), dim3(HB * 32), smem, stream,
                           true, qa, (const T*)pages, row, bt, bt_stride, token_seq, positions, part_o, part_ml, nsplit, H,
                           R, dk, ps, scale, kw, span));
@@ -357,7 +358,7 @@ int pick_attention(int R, const float* qa, const void* pages, int row, const int
 // latents of 512; the two warps of a row group then split the tile's keys for the scores and share the weights).  Key tile j covers the positions [32j, 32j + 32): its rows come into shared memory by cp.async as
 // they lie in the pages (rows nobody sees are zero-filled), the next tile's while the current one is used, and serve
 // twice: as keys (all R + dr columns) and, read transposed, as values (the first R columns).  The absorbed queries are
-// taken as hi + lo, two bfloat16 terms (hi alone where shared memory cannot hold both: rows beyond 520 columns), so the
+// taken as hi + lo, two bfloat16 terms (hi alone where shared memory cannot hold both: rows beyond 568 columns), so the
 // scores keep about 16 bits of them; scores, mask and the online softmax are 32-bit (scores in units of ln 2, ex2.approx); the
 // weights enter the second product as p = hi + lo, two bfloat16 terms, so they keep about 16 bits; output sums 32-bit.
 constexpr int MQ = 64, MK = 32;
@@ -586,7 +587,7 @@ int launch_mma_q(const float* qa, const void* pages, int row, const int* bt, int
     const size_t smem = (size_t)((QL ? 2 : 1) * MQ + 2 * MK) * (dk + 8) * 2 + (CW == 2 ? PAIR_BYTES : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        MLLM_CUDA(cudaFuncSetAttribute(latent_mma_kernel<NO, CW, QL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        MLLM_CUDA(cudaFuncSetAttribute(latent_mma_kernel<NO, CW, QL>, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM));
         raised = true;
     }
     MLLM_CUDA(mllm_launch(latent_mma_kernel<NO, CW, QL>, dim3(H, n_tiles), dim3(128 * CW), smem, stream, true, qa,
@@ -597,7 +598,7 @@ int launch_mma_q(const float* qa, const void* pages, int row, const int* bt, int
 template <int NO, int CW>
 int launch_mma(const float* qa, const void* pages, int row, const int* bt, int bt_stride, const int* tiles, int n_tiles,
                const int* positions, float* out, int H, int R, int dk, int ps, float scale, cudaStream_t stream) {
-    if ((size_t)(2 * MQ + 2 * MK) * (dk + 8) * 2 + (CW == 2 ? PAIR_BYTES : 0) <= 200 * 1024)
+    if ((size_t)(2 * MQ + 2 * MK) * (dk + 8) * 2 + (CW == 2 ? PAIR_BYTES : 0) <= MAX_SMEM)
         return launch_mma_q<NO, CW, 1>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
     return launch_mma_q<NO, CW, 0>(qa, pages, row, bt, bt_stride, tiles, n_tiles, positions, out, H, R, dk, ps, scale, stream);
 }
@@ -792,7 +793,7 @@ MLLM_EXPORT int mllm_latent_attention(const float* qa, const void* pages, int ro
 // 1 if the tensor-core kernel for prompt portions takes these sizes (a bfloat16 cache is the caller's to check).
 MLLM_EXPORT int mllm_latent_mma_ok(int R, int dk, int row) {
     return R > 0 && R % 8 == 0 && R <= MAX_R && dk % 16 == 0 && dk >= R && row >= dk && row % 8 == 0 &&
-           (size_t)(MQ + 2 * MK) * (dk + 8) * 2 + PAIR_BYTES <= 200 * 1024;
+           (size_t)(MQ + 2 * MK) * (dk + 8) * 2 + PAIR_BYTES <= MAX_SMEM;
 }
 
 // Prompt portions with a bfloat16 cache: tiles [n_tiles][3] = (request, first flat token, rows <= 64).

@@ -281,8 +281,8 @@ def test_latent_attention_on_tensor_cores(ops, H, R, dr, page):
         ops.latent_attention(qa, pages, bt, ctx, out, heads=H, rank=R, scale=scale)
         assert ops.attention_launches.get("latent_mma", 0) == n0 + 1
         want = _latent_want(ctx, qa, dense, seqs, H, R, scale)
-        # queries enter as hi + lo bfloat16 terms; rows beyond 520 columns leave no room for the lo term
-        assert _rel(out, want) < (2e-4 if R + dr + 8 <= 520 else 3e-2)
+        # queries enter as hi + lo bfloat16 terms; rows beyond 568 columns leave no room for the lo term
+        assert _rel(out, want) < (2e-4 if R + dr <= 568 else 3e-2)
         ref = torch.zeros(ctx.T, H * R, device=DEV)
         ops.latent_attention(qa, pages, bt, ctx, ref, heads=H, rank=R, scale=scale, impl="split")
         assert _rel(ref, want) < 2e-5
