@@ -1,4 +1,4 @@
-// A routed feed-forward (mixture of experts) without a host round trip:
+// A routed feed-forward (mixture of experts) in which the host reads nothing back:
 //
 //   moe_route       a warp per token: router logits in 32-bit, softmax over all experts, the best `keep` of `n_groups`
 //                   equal groups of neighbouring experts (a group's score is its largest), the `top` best experts inside
